@@ -22,13 +22,14 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.base import CacheSpec, KVSpec, StateSpec
+from ..parts.base import CacheSpec, KVSpec, StateSpec, split_cache_spec
 from .pages import PAGE_SIZE, CacheFull, PagePool
 
 
 class KVGroup:
-    """Storage of all places that share one KVSpec: per place K and V of shape
-    [n_pages, n_kv_heads, PAGE_SIZE, head_dim]."""
+    """Storage of all places that share one KVSpec: per place K of shape
+    [n_pages, n_kv_heads, PAGE_SIZE, head_dim] and V of the same shape unless the
+    spec gives the values heads or a size of their own."""
 
     def __init__(self, spec: KVSpec, places: Sequence[int], n_pages: int, n_slots: int,
                  dtype: torch.dtype, device: torch.device):
@@ -36,8 +37,9 @@ class KVGroup:
         self.pool = PagePool(n_pages)
         self.page_size = PAGE_SIZE
         shape = (n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
+        v_shape = (n_pages, spec.v_heads, PAGE_SIZE, spec.v_dim)
         self.k: Dict[int, torch.Tensor] = {p: torch.zeros(shape, dtype=dtype, device=device) for p in self.places}
-        self.v: Dict[int, torch.Tensor] = {p: torch.zeros(shape, dtype=dtype, device=device) for p in self.places}
+        self.v: Dict[int, torch.Tensor] = {p: torch.zeros(v_shape, dtype=dtype, device=device) for p in self.places}
         # pages[slot][i] holds keys [i*PAGE, (i+1)*PAGE); -1 once a window has passed it
         self.pages: List[List[int]] = [[] for _ in range(n_slots)]
 
@@ -53,13 +55,15 @@ class KVGroup:
 
     def release_passed(self, slot: int, length: int) -> None:
         """With a window w, the next query (position `length`) reads keys
-        > length - w; pages wholly at or below that are given back."""
+        > length - w; pages wholly at or below that are given back, except the
+        pages that hold one of the first `keep_first` keys, which every query reads."""
         w = self.spec.window
         if w <= 0:
             return
         pages = self.pages[slot]
         first_needed = max(0, length - w + 1)
-        for i in range(min(len(pages), first_needed // PAGE_SIZE)):
+        kept_pages = (self.spec.keep_first + PAGE_SIZE - 1) // PAGE_SIZE
+        for i in range(kept_pages, min(len(pages), first_needed // PAGE_SIZE)):
             if pages[i] >= 0:
                 self.pool.give_back(pages[i])
                 pages[i] = -1
@@ -108,12 +112,14 @@ class SequenceCache:
         by_spec: Dict[KVSpec, List[int]] = {}
         self.states: Dict[int, torch.Tensor] = {}
         for place, spec in enumerate(place_specs):
-            if isinstance(spec, KVSpec):
-                by_spec.setdefault(spec, []).append(place)
-            elif isinstance(spec, StateSpec):
-                self.states[place] = torch.zeros((self.n_slots, *spec.shape), dtype=torch.float32, device=device)
-            elif spec is not None:
-                raise TypeError(f"place {place}: unknown cache spec {spec!r}")
+            try:
+                kv, state = split_cache_spec(spec)
+            except TypeError as e:
+                raise TypeError(f"place {place}: {e}") from None
+            if kv is not None:
+                by_spec.setdefault(kv, []).append(place)
+            if state is not None:
+                self.states[place] = torch.zeros((self.n_slots, *state.shape), dtype=torch.float32, device=device)
         self.groups: List[KVGroup] = [KVGroup(spec, places, n_pages, self.n_slots, dtype, device)
                                       for spec, places in by_spec.items()]
         self.group_of_place: Dict[int, int] = {p: gi for gi, g in enumerate(self.groups) for p in g.places}

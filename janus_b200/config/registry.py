@@ -52,6 +52,12 @@ def architecture_name(config_dict: Dict[str, Any]) -> str:
     """`architectures[0]`; a config without the key is taken as Llama, which
     the reference accepts too (config.rs:183)."""
     archs = config_dict.get("architectures")
+    if archs is None and "architecture" in config_dict:
+        # the singular key with one name, as some designs write it
+        name = config_dict["architecture"]
+        if not isinstance(name, str):
+            raise ConfigError(f"key 'architecture' must be a string, got {name!r}")
+        return name
     if archs is None or archs == []:
         return DEFAULT_ARCHITECTURE
     if not isinstance(archs, list) or not isinstance(archs[0], str):

@@ -1,0 +1,264 @@
+// Differential attention over the paged cache, with a short causal convolution on the
+// projected q, k and v, rotation of a leading part of every vector, a sliding window that
+// keeps a sequence's first keys, and the per-head unit norm of the combined maps.
+//
+// A query head has two maps, each an attention of its own over the same values:
+//   q row: [head][map][d]   k row: [kv head][map][d]   v row: [kv head][e]
+// The key cache is [page][2 G][PAGE][d] (a kv head's two maps are neighbouring "heads"),
+// the value cache [page][G][PAGE][e]; block_table[seq][i] is the page of keys [i PAGE, (i+1) PAGE).
+//
+//   conv_rope_cache:  y_t = sum_j w[c, j] u_(t - taps + 1 + j) per channel c, where u before the
+//                     step's first token comes from the sequence's state (its last taps - 1
+//                     projected values) and is zero before the sequence's start; then the first
+//                     `rot` dimensions of every q and k vector turn by the token's position (pairs
+//                     (i, i + rot/2), cos and sin from a table); q goes out in float32, k and v
+//                     into the cache.
+//   conv_state_update: the state takes the step's last projected values.
+//   diff_attention:   one warp per (token, query head); both maps' online softmax over the visible
+//                     keys j <= i with (i - j < window or j < keep_first), in chunks of 32 keys that
+//                     start at multiples of 32 of the key index (so the result does not depend on how
+//                     a sequence was cut into steps); o = a1 - lambda a2, divided by its root mean
+//                     square over the head's e values (eps inside the root), times out_scale.
+// Scores, softmax weights and the sums are float32 whatever the cache holds.
+#include <math_constants.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename TC>
+__global__ void conv_rope_cache_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w, int taps,
+                                       const float* __restrict__ conv_state, const int* __restrict__ token_seq,
+                                       const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                       const int* __restrict__ positions, const float* __restrict__ cos_sin, int rot,
+                                       float* __restrict__ q_out, const int* __restrict__ dest, TC* __restrict__ k_cache,
+                                       TC* __restrict__ v_cache, int H, int G, int d, int e, int page_size) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = token_seq[t];
+  const int local = t - q_start[seq];                 // tokens of this sequence before t within the step
+  const int Cq = H * 2 * d, Ck = G * 2 * d, Cv = G * e, C = Cq + Ck + Cv;
+  const float* st = conv_w ? conv_state + (size_t)seq_slot[seq] * (taps - 1) * C : nullptr;
+  const int half = rot >> 1;
+  const float* cs = cos_sin ? cos_sin + (size_t)positions[t] * half * 2 : nullptr;
+  const int dst = dest[t];
+  const int page = dst / page_size, off = dst % page_size;
+
+  auto convolved = [&](int c) -> float {
+    if (!conv_w) return proj[(size_t)t * ld + c];
+    float y = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;                  // how many tokens before t
+      float u;
+      if (back <= local) u = proj[(size_t)(t - back) * ld + c];
+      else u = st[(size_t)(taps - 1 - (back - local)) * C + c];
+      y = fmaf(conv_w[(size_t)c * taps + j], u, y);
+    }
+    return y;
+  };
+  auto put = [&](int c, float y) {
+    if (c < Cq) {
+      q_out[(size_t)t * Cq + c] = y;
+    } else if (c < Cq + Ck) {
+      const int kc = c - Cq, vec = kc / d, i = kc % d;
+      k_cache[(((size_t)page * 2 * G + vec) * page_size + off) * d + i] = jb::from_f32<TC>(y);
+    } else {
+      const int vc = c - Cq - Ck, g = vc / e, i = vc % e;
+      v_cache[(((size_t)page * G + g) * page_size + off) * e + i] = jb::from_f32<TC>(y);
+    }
+  };
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    if (c >= Cq + Ck || cs == nullptr) {
+      put(c, convolved(c));
+      continue;
+    }
+    const int i = (c < Cq ? c : c - Cq) % d;
+    if (i >= rot) {
+      put(c, convolved(c));
+    } else if (i < half) {
+      const float a = convolved(c), b = convolved(c + half);
+      const float co = cs[2 * i], si = cs[2 * i + 1];
+      put(c, a * co - b * si);
+      put(c + half, b * co + a * si);
+    }
+  }
+}
+
+__global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld, float* __restrict__ conv_state, int taps,
+                                         const int* __restrict__ q_start, const int* __restrict__ seq_slot, int C) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int seq = blockIdx.x;
+  const int t0 = q_start[seq], n = q_start[seq + 1] - t0;
+  float* st = conv_state + (size_t)seq_slot[seq] * (taps - 1) * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    for (int i = 0; i < taps - 1; ++i) {           // new[i] is the value n - (taps - 1) + i tokens into the step
+      const int li = n - (taps - 1) + i;
+      st[(size_t)i * C + c] = li >= 0 ? proj[(size_t)(t0 + li) * ld + c] : st[(size_t)(i + n) * C + c];
+    }
+  }
+}
+
+constexpr int WARPS = 4;
+
+// EJ: value columns a lane holds (e <= 32 EJ)
+template <typename TC, typename TO, int EJ>
+__global__ void __launch_bounds__(WARPS * 32) diff_attention_kernel(
+    const float* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, TO* __restrict__ out,
+    const int* __restrict__ block_table, const int* __restrict__ token_seq, const int* __restrict__ positions, int T, int H,
+    int G, int d, int e, int page_size, int max_pages, int window, int keep_first, float scale, float lambda, float eps,
+    float out_scale) {
+  extern __shared__ float q_s[];                     // [WARPS][2 d]
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * WARPS + warp;
+  if (item >= (long long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const int g = h / (H / G);
+  const int pos = positions[t];
+  const int* pages = block_table + (size_t)token_seq[t] * max_pages;
+  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  float* qw = q_s + warp * 2 * d;
+  for (int i = lane; i < 2 * d; i += 32) qw[i] = q[((size_t)t * H + h) * 2 * d + i];
+  __syncwarp();
+
+  float m1 = -CUDART_INF_F, l1 = 0.0f, m2 = -CUDART_INF_F, l2 = 0.0f;
+  float a1[EJ], a2[EJ];
+#pragma unroll
+  for (int j = 0; j < EJ; ++j) a1[j] = a2[j] = 0.0f;
+
+  auto chunk = [&](int c0) {
+    const int key = c0 + lane;
+    const bool valid = key <= pos && (key >= kstart || key < keep_first);
+    float s1 = -CUDART_INF_F, s2 = -CUDART_INF_F;
+    if (valid) {
+      const int page = pages[key / page_size], row = key % page_size;
+      const TC* k1 = k_cache + (((size_t)page * 2 * G + 2 * g) * page_size + row) * d;
+      const TC* k2 = k1 + (size_t)page_size * d;
+      float d1 = 0.0f, d2 = 0.0f;
+      for (int i = 0; i < d; ++i) {
+        d1 = fmaf(qw[i], jb::to_f32(k1[i]), d1);
+        d2 = fmaf(qw[d + i], jb::to_f32(k2[i]), d2);
+      }
+      s1 = d1 * scale;
+      s2 = d2 * scale;
+    }
+    const float n1 = fmaxf(m1, jb::warp_max(s1)), n2 = fmaxf(m2, jb::warp_max(s2));
+    if (n1 == -CUDART_INF_F) return;                 // no visible key in this chunk or before (uniform)
+    const float p1 = valid ? expf(s1 - n1) : 0.0f, p2 = valid ? expf(s2 - n2) : 0.0f;
+    const float c1 = expf(m1 - n1), c2 = expf(m2 - n2);   // exp(-inf) = 0 before the first key
+    l1 = l1 * c1 + jb::warp_sum(p1);
+    l2 = l2 * c2 + jb::warp_sum(p2);
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) {
+      a1[j] *= c1;
+      a2[j] *= c2;
+    }
+    const unsigned seen = __ballot_sync(0xffffffffu, valid);
+    for (int kk = 0; kk < 32; ++kk) {
+      if (!((seen >> kk) & 1u)) continue;            // uniform across the warp
+      const int key2 = c0 + kk;
+      const int page = pages[key2 / page_size], row = key2 % page_size;
+      const TC* vr = v_cache + (((size_t)page * G + g) * page_size + row) * e;
+      const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
+#pragma unroll
+      for (int j = 0; j < EJ; ++j) {
+        const int c = lane + 32 * j;
+        if (c < e) {
+          const float v = jb::to_f32(vr[c]);
+          a1[j] = fmaf(w1, v, a1[j]);
+          a2[j] = fmaf(w2, v, a2[j]);
+        }
+      }
+    }
+    m1 = n1;
+    m2 = n2;
+  };
+
+  const int first_window_chunk = (kstart / 32) * 32;
+  const int kept = min(keep_first, kstart);          // kept keys that the window has left behind
+  for (int c0 = 0; c0 < kept && c0 < first_window_chunk; c0 += 32) chunk(c0);
+  for (int c0 = first_window_chunk; c0 <= pos; c0 += 32) chunk(c0);
+
+  float o[EJ], ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < EJ; ++j) {
+    o[j] = a1[j] / l1 - lambda * (a2[j] / l2);
+    if (lane + 32 * j < e) ss += o[j] * o[j];
+  }
+  ss = jb::warp_sum(ss);
+  const float rms = sqrtf(ss / (float)e + eps);
+  TO* orow = out + ((size_t)t * H + h) * e;
+#pragma unroll
+  for (int j = 0; j < EJ; ++j) {
+    const int c = lane + 32 * j;
+    if (c < e) orow[c] = jb::from_f32<TO>((o[j] / rms) * out_scale);
+  }
+}
+
+}  // namespace
+
+// proj: float32 [T, ld], columns [q: H 2 d | k: G 2 d | v: G e]; conv_w: float32 [C, taps] or null (no convolution);
+// conv_state: float32 [slots, taps - 1, C]; cos_sin: float32 [positions, rot / 2, 2] or null (no rotation);
+// q_out: float32 [T, H 2 d]; dest[t] = page * page_size + row of token t in the caches (cache_dtype).
+JB_EXPORT int jb_conv_rope_cache(const float* proj, int ld, const float* conv_w, int taps, const float* conv_state,
+                                 const int* token_seq, const int* q_start, const int* seq_slot, const int* positions,
+                                 const float* cos_sin, int rot, float* q_out, const int* dest, void* k_cache, void* v_cache,
+                                 int cache_dtype, int T, int H, int G, int d, int e, int page_size, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(rot % 2 != 0 || rot > d || rot < 0, "conv_rope_cache: %d rotated dimensions do not fit vectors of %d", rot, d);
+  JB_REFUSE(conv_w != nullptr && taps < 1, "conv_rope_cache: %d taps", taps);
+  const int C = H * 2 * d + G * 2 * d + G * e;
+  jb::Launch cfg(dim3(T), dim3(C >= 1024 ? 256 : 128), 0, stream);
+  if (cache_dtype == JB_F32)
+    return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<float>, proj, ld, conv_w, taps, conv_state, token_seq,
+                                   q_start, seq_slot, positions, cos_sin, rot, q_out, dest, (float*)k_cache,
+                                   (float*)v_cache, H, G, d, e, page_size);
+  if (cache_dtype == JB_BF16)
+    return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<bf16>, proj, ld, conv_w, taps, conv_state, token_seq,
+                                   q_start, seq_slot, positions, cos_sin, rot, q_out, dest, (bf16*)k_cache, (bf16*)v_cache,
+                                   H, G, d, e, page_size);
+  return JB_ERR_BAD_DTYPE;
+}
+
+JB_EXPORT int jb_conv_state_update(const float* proj, int ld, float* conv_state, int taps, const int* q_start,
+                                   const int* seq_slot, int n_seqs, int C, cudaStream_t stream) {
+  if (n_seqs <= 0 || taps <= 1) return 0;
+  jb::Launch cfg(dim3(n_seqs, (C + 255) / 256), dim3(256), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, conv_state_update_kernel, proj, ld, conv_state, taps, q_start, seq_slot, C);
+}
+
+// q: float32 [T, H 2 d]; out: [T, H e] in out_dtype; caches in cache_dtype; window 0 = every key.
+JB_EXPORT int jb_diff_attention(const float* q, const void* k_cache, const void* v_cache, int cache_dtype, void* out,
+                                int out_dtype, const int* block_table, const int* token_seq, const int* positions, int T,
+                                int H, int G, int d, int e, int page_size, int max_pages, int window, int keep_first,
+                                float scale, float lambda, float eps, float out_scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(G <= 0 || H % G != 0, "diff_attention: %d heads are not a multiple of %d key/value heads", H, G);
+  JB_REFUSE(e < 1 || e > 256 || d < 1 || d > 1024, "diff_attention: sizes %d (keys) and %d (values) are not supported", d, e);
+  const long long items = (long long)T * H;
+  const size_t smem = (size_t)WARPS * 2 * d * sizeof(float);
+  jb::Launch cfg(dim3((unsigned)((items + WARPS - 1) / WARPS)), dim3(WARPS * 32), smem, stream);
+  cudaError_t err;
+#define JB_LAUNCH_DA(TC, TO, EJ)                                                                                     \
+  err = cudaLaunchKernelEx(&cfg.c, diff_attention_kernel<TC, TO, EJ>, q, (const TC*)k_cache, (const TC*)v_cache,     \
+                           (TO*)out, block_table, token_seq, positions, T, H, G, d, e, page_size, max_pages, window, \
+                           keep_first, scale, lambda, eps, out_scale)
+#define JB_LAUNCH_DA_E(TC, TO)            \
+  do {                                    \
+    if (e <= 64) JB_LAUNCH_DA(TC, TO, 2); \
+    else if (e <= 128) JB_LAUNCH_DA(TC, TO, 4); \
+    else JB_LAUNCH_DA(TC, TO, 8);         \
+  } while (0)
+  if (cache_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_DA_E(float, float);
+  else if (cache_dtype == JB_BF16 && out_dtype == JB_BF16) JB_LAUNCH_DA_E(bf16, bf16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_DA_E
+#undef JB_LAUNCH_DA
+  return (int)err;
+}

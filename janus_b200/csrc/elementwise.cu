@@ -344,3 +344,53 @@ JB_EXPORT int jb_pack_weight_bf16(const void* src, int N, int K, void* dst, cuda
                                                                              n_chunks);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// A gated activation with clamped branches: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha g) * (u + 1).  gate_up: float32 rows of ld floats, the gate of feature c in
+// column c, its up value in column up_col + c; out: [T, I] in out_dtype.
+// A scale and a soft cap on a float32 tensor in place: y = cap * tanh(x * scale / cap) (cap <= 0: y = x * scale).
+// ---------------------------------------------------------------------------
+namespace {
+template <typename TO>
+__global__ void clamped_glu_kernel(const float* __restrict__ gate_up, int ld, int up_col, TO* __restrict__ out, int I,
+                                   float limit, float alpha, size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / I, c = i % I;
+  const float g = fminf(gate_up[t * ld + c], limit);
+  const float u = fminf(fmaxf(gate_up[t * ld + up_col + c], -limit), limit);
+  out[i] = jb::from_f32<TO>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+}
+
+__global__ void scale_softcap_kernel(float* __restrict__ x, float scale, float cap, size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = x[i] * scale;
+  x[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+}
+}  // namespace
+
+JB_EXPORT int jb_clamped_glu(const float* gate_up, int ld, int up_col, void* out, int out_dtype, int T, int I, float limit,
+                             float alpha, cudaStream_t stream) {
+  const size_t n = (size_t)T * I;
+  if (n == 0) return 0;
+  JB_REFUSE(ld < up_col + I || up_col < I, "clamped_glu: rows of %d floats do not hold %d gate and %d up features from column %d",
+            ld, I, I, up_col);
+  jb::Launch cfg(dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream);
+  if (out_dtype == JB_F32)
+    return (int)cudaLaunchKernelEx(&cfg.c, clamped_glu_kernel<float>, gate_up, ld, up_col, (float*)out, I, limit, alpha, n);
+  if (out_dtype == JB_BF16)
+    return (int)cudaLaunchKernelEx(&cfg.c, clamped_glu_kernel<bf16>, gate_up, ld, up_col, (bf16*)out, I, limit, alpha, n);
+  return JB_ERR_BAD_DTYPE;
+}
+
+JB_EXPORT int jb_scale_softcap(float* x, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  jb::Launch cfg(dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, scale_softcap_kernel, x, scale, cap, (size_t)n);
+}

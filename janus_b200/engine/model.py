@@ -26,6 +26,9 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device):
         self.spec, self.dtype, self.device = spec, dtype, device
         self.hidden_size, self.vocab_size = spec.hidden_size, spec.vocab_size
+        self.streams = int(spec.residual_streams)
+        if self.streams < 1:
+            raise ValueError(f"a model has at least one residual stream, got {self.streams}")
         self.layers = []
         self._layer_part_objs: List[Dict[str, object]] = []
         for ls in spec.layers:
@@ -94,9 +97,14 @@ class DecoderModel:
 
     def _forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
         T = ctx.n_tokens
-        residual = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
-        ops.embed_gather(self.embedding, ctx.token_ids, residual, ctx.feedback,
-                         ctx.seq_slot if ctx.feedback is not None else None)
+        residual = ctx.workspace.get("residual", (T, self.streams * self.hidden_size), torch.float32)
+        if self.streams == 1:
+            ops.embed_gather(self.embedding, ctx.token_ids, residual, ctx.feedback,
+                             ctx.seq_slot if ctx.feedback is not None else None)
+        else:
+            # every stream starts as the embedding
+            ops.embed_streams(self.embedding, ctx.token_ids, residual, self.streams, ctx.feedback,
+                              ctx.seq_slot if ctx.feedback is not None else None)
         for transform in self.embedding_transforms:
             transform.forward(residual, ctx)
         for place, entry in enumerate(self.schedule):
@@ -107,7 +115,10 @@ class DecoderModel:
         if n_want == 0:
             return
         z = ctx.workspace.get("final_normed", (n_want, self.hidden_size), self.dtype)
-        self.final_norm.forward(residual, z, row_index=want_rows)
+        if self.streams == 1:
+            self.final_norm.forward(residual, z, row_index=want_rows)
+        else:
+            self.final_norm.forward_streams(residual, self.streams, None, z, row_index=want_rows)   # the streams' sum
         self.head.forward(z, logits)
         for transform in self.logit_transforms:
             transform.forward(logits, ctx)

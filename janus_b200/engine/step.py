@@ -76,12 +76,11 @@ class StepContext:
     def cache_view(self, place: int) -> CacheView:
         cache = self.cache
         gi = cache.group_of_place.get(place)
+        state = cache.states.get(place)
         if gi is not None:
             g = cache.groups[gi]
-            return CacheView(k=g.k[place], v=g.v[place], group=self.groups[gi])
-        if place in cache.states:
-            return CacheView(state=cache.states[place])
-        return CacheView()
+            return CacheView(k=g.k[place], v=g.v[place], group=self.groups[gi], state=state)
+        return CacheView(state=state)
 
 
 def _pad4(n: int) -> int:

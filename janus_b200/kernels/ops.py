@@ -63,6 +63,11 @@ _SIGNATURES = {
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
     "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
+    "jb_streams_rmsnorm": "pppipifpiiipp", "jb_streams_mix": "ppppiiip", "jb_embed_streams": "pippiiippp",
+    "jb_lightning_scan": "piiiipppppiiiip", "jb_gated_rmsnorm": "ppipifpiiip",
+    "jb_conv_rope_cache": "pipippppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
+    "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
+    "jb_clamped_glu": "piipiiiffp", "jb_scale_softcap": "plffp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
            "f": ctypes.c_float}
@@ -887,3 +892,172 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
         scale, _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")
+
+
+# -- several residual streams per token -------------------------------------------------
+def embed_streams(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, streams: int,
+                  feedback: Optional[torch.Tensor] = None, token_slot: Optional[torch.Tensor] = None) -> None:
+    """out[t, s, :] = float32(table[ids[t], :]) for every stream s (out: [T, streams * H])."""
+    T = out.shape[0]
+    H = out.shape[1] // streams
+    _need(table, "embed table")
+    _need(ids, "token ids", torch.int32, (T,))
+    _need(out, "embed out", torch.float32, (T, streams * H))
+    if table.shape[1] != H:
+        raise KernelError(f"embed: table width {table.shape[1]} != output width {H}")
+    _check(_lib("hyper").jb_embed_streams(
+        _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), T, H, int(streams), _ptr(feedback),
+        _ptr(token_slot), _stream()), "embed_streams")
+
+
+def streams_rmsnorm(x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], gamma: torch.Tensor, eps: float,
+                    out: torch.Tensor, row_index: Optional[torch.Tensor] = None,
+                    clear: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(sum_s weights[s] * x[row, s, :]) * gamma with x float32 [*, streams * H]; weights None:
+    the plain sum.  `clear`: a float32 [rows, H] tensor whose rows are set to zero by the same launch."""
+    rows, H = out.shape
+    _need(x, "streams x", torch.float32)
+    if x.dim() != 2 or x.shape[1] != streams * H:
+        raise KernelError(f"streams_rmsnorm: input of shape {tuple(x.shape)} is not [*, {streams} * {H}]")
+    _need(gamma, "streams gamma", None, (H,))
+    _need(out, "streams out")
+    if weights is not None:
+        _need(weights, "stream weights", torch.float32, (streams,))
+    if row_index is not None:
+        _need(row_index, "streams row_index", torch.int32, (rows,))
+    elif x.shape[0] < rows:
+        raise KernelError("streams_rmsnorm: fewer input rows than output rows")
+    if clear is not None:
+        _need(clear, "streams clear", torch.float32, (rows, H))
+    _check(_lib("hyper").jb_streams_rmsnorm(
+        _ptr(x), _ptr(row_index), _ptr(weights), int(streams), _ptr(gamma), dtype_code(gamma.dtype), eps, _ptr(out),
+        dtype_code(out.dtype), rows, H, _ptr(clear), _stream()), "streams_rmsnorm")
+
+
+def streams_mix(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights: torch.Tensor, streams: int) -> None:
+    """x[t, to, :] <- sum_s mix[s, to] * x[t, s, :] + out_weights[to] * y[t, :], every stream from the old ones."""
+    T, H = y.shape
+    _need(x, "streams x", torch.float32, (T, streams * H))
+    _need(y, "sublayer output", torch.float32)
+    _need(mix, "stream mix", torch.float32, (streams, streams))
+    _need(out_weights, "stream out weights", torch.float32, (streams,))
+    _check(_lib("hyper").jb_streams_mix(_ptr(x), _ptr(y), _ptr(mix), _ptr(out_weights), T, int(streams), H, _stream()),
+           "streams_mix")
+
+
+# -- linear attention with decay ----------------------------------------------------------
+def lightning_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, out: torch.Tensor, state: torch.Tensor,
+                   q_start: torch.Tensor, seq_slot: torch.Tensor, decay: torch.Tensor, n_seqs: int, heads: int,
+                   dim: int, vdim: int) -> None:
+    """Per sequence and head S <- decay S + silu(k_t) silu(v_t)^T, out_t = S^T silu(q_t) over the step's tokens in
+    order; proj float32 [T, ld] holds the raw q, k, v at the given columns; state float32 [slots, heads, dim, vdim]."""
+    T = proj.shape[0]
+    _need(proj, "lightning projections", torch.float32)
+    _need(out, "lightning out", torch.float32, (T, heads * vdim))
+    _need(state, "lightning state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"lightning_scan: state of shape {tuple(state.shape)} is not [slots, {heads}, {dim}, {vdim}]")
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
+    _need(decay, "decay", torch.float32, (heads,))
+    if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim) > proj.shape[1]:
+        raise KernelError("lightning_scan: the projections' columns reach past the rows")
+    _check(_lib("lightning").jb_lightning_scan(
+        _ptr(proj), proj.shape[1], int(q_col), int(k_col), int(v_col), _ptr(out), _ptr(state), _ptr(q_start),
+        _ptr(seq_slot), _ptr(decay), n_seqs, heads, dim, vdim, _stream()), "lightning_scan")
+
+
+def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate); o float32 [T, N], gate a float32 view [T, N] of
+    rows that may be wider (its row stride is passed on)."""
+    T, N = o.shape
+    _need(o, "gated norm input", torch.float32)
+    _need(weight, "gated norm weight", None, (N,))
+    _need(out, "gated norm out", None, (T, N))
+    if _checks[0] and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, N) or gate.stride(1) != 1):
+        raise KernelError("gated_rmsnorm: the gate must be float32 [T, N] with unit column stride")
+    _check(_lib("lightning").jb_gated_rmsnorm(
+        _ptr(o), _ptr(weight), dtype_code(weight.dtype), _ptr(gate), gate.stride(0), eps, _ptr(out),
+        dtype_code(out.dtype), T, N, _stream()), "gated_rmsnorm")
+
+
+# -- differential attention -----------------------------------------------------------------
+def conv_rope_cache(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, conv_state: Optional[torch.Tensor],
+                    token_seq: torch.Tensor, q_start: torch.Tensor, seq_slot: torch.Tensor, positions: torch.Tensor,
+                    cos_sin: Optional[torch.Tensor], rot: int, q_out: torch.Tensor, dest: torch.Tensor,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                    page_size: int) -> None:
+    """Short causal convolution over time on every channel of the projected q, k, v (float32 [T, C]), rotation of
+    the first `rot` dimensions of every q and k vector, q out in float32, k and v into the paged caches."""
+    T = proj.shape[0]
+    C = heads * 2 * dim + kv_heads * 2 * dim + kv_heads * vdim
+    _need(proj, "projections", torch.float32, (T, C))
+    _need(q_out, "q out", torch.float32, (T, heads * 2 * dim))
+    _need(dest, "cache rows", torch.int32, (T,))
+    _need(token_seq, "token_seq", torch.int32, (T,))
+    _need(positions, "positions", torch.int32, (T,))
+    _need(k_cache, "k cache")
+    _need(v_cache, "v cache", k_cache.dtype)
+    if tuple(k_cache.shape[1:]) != (2 * kv_heads, page_size, dim) or tuple(v_cache.shape[1:]) != (kv_heads, page_size, vdim):
+        raise KernelError(f"conv_rope_cache: caches of shapes {tuple(k_cache.shape)}, {tuple(v_cache.shape)} do not fit")
+    if conv_w is not None:
+        _need(conv_w, "conv weights", torch.float32, (C, taps))
+    if conv_w is not None and taps > 1:
+        _need(conv_state, "conv state", torch.float32)
+        if tuple(conv_state.shape[1:]) != (taps - 1, C):
+            raise KernelError(f"conv_rope_cache: state of shape {tuple(conv_state.shape)} is not [slots, {taps - 1}, {C}]")
+    if cos_sin is not None:
+        _need(cos_sin, "rotation table", torch.float32)
+        if tuple(cos_sin.shape[1:]) != (rot // 2, 2):
+            raise KernelError(f"conv_rope_cache: table of shape {tuple(cos_sin.shape)} does not fit {rot} rotated dimensions")
+    _check(_lib("diff_attention").jb_conv_rope_cache(
+        _ptr(proj), proj.shape[1], _ptr(conv_w), int(taps), _ptr(conv_state), _ptr(token_seq), _ptr(q_start),
+        _ptr(seq_slot), _ptr(positions), _ptr(cos_sin), int(rot), _ptr(q_out), _ptr(dest), _ptr(k_cache), _ptr(v_cache),
+        dtype_code(k_cache.dtype), T, heads, kv_heads, dim, vdim, page_size, _stream()), "conv_rope_cache")
+
+
+def conv_state_update(proj: torch.Tensor, conv_state: torch.Tensor, taps: int, q_start: torch.Tensor,
+                      seq_slot: torch.Tensor, n_seqs: int) -> None:
+    """The convolution's state of every sequence of the step takes the last taps - 1 projected values."""
+    _need(proj, "projections", torch.float32)
+    _need(conv_state, "conv state", torch.float32)
+    _check(_lib("diff_attention").jb_conv_state_update(
+        _ptr(proj), proj.shape[1], _ptr(conv_state), int(taps), _ptr(q_start), _ptr(seq_slot), n_seqs, proj.shape[1],
+        _stream()), "conv_state_update")
+
+
+def diff_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                   block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int,
+                   dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float, lam: float, eps: float,
+                   out_scale: float) -> None:
+    """Two softmax maps per head over the same values, o = a1 - lam a2, unit norm over the head, times out_scale."""
+    T = q.shape[0]
+    _need(q, "attention q", torch.float32, (T, heads * 2 * dim))
+    _need(out, "attention out", k_cache.dtype, (T, heads * vdim))
+    _need(k_cache, "k cache")
+    _need(v_cache, "v cache", k_cache.dtype)
+    _need(block_table, "block table", torch.int32)
+    _need(token_seq, "token_seq", torch.int32, (T,))
+    _need(positions, "positions", torch.int32, (T,))
+    _check(_lib("diff_attention").jb_diff_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(out), dtype_code(out.dtype),
+        _ptr(block_table), _ptr(token_seq), _ptr(positions), T, heads, kv_heads, dim, vdim, page_size,
+        block_table.shape[1], int(window), int(keep_first), scale, lam, eps, out_scale, _stream()), "diff_attention")
+
+
+# -- a gated activation with clamped branches; scale and soft cap -------------------------------
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, up_col: int, limit: float, alpha: float) -> None:
+    """out[t, c] = g sigmoid(alpha g) (u + 1), g = min(gate_up[t, c], limit), u = clamp(gate_up[t, up_col + c], +-limit)."""
+    T, I = out.shape
+    _need(gate_up, "gate/up", torch.float32)
+    _need(out, "activation out")
+    if gate_up.dim() != 2 or gate_up.shape[0] != T:
+        raise KernelError(f"clamped_glu: input of shape {tuple(gate_up.shape)} does not hold {T} rows")
+    _check(_lib("elementwise").jb_clamped_glu(_ptr(gate_up), gate_up.shape[1], int(up_col), _ptr(out),
+                                              dtype_code(out.dtype), T, I, limit, alpha, _stream()), "clamped_glu")
+
+
+def scale_softcap(x: torch.Tensor, scale: float, cap: float) -> None:
+    """x <- cap * tanh(x * scale / cap) in place (cap <= 0: x * scale); float32."""
+    _need(x, "logits", torch.float32)
+    _check(_lib("elementwise").jb_scale_softcap(_ptr(x), x.numel(), scale, cap, _stream()), "scale_softcap")

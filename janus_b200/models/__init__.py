@@ -1,1 +1,1 @@
-from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import llama, zivitar  # noqa: F401  (registers LlamaForCausalLM and Zivitar)

@@ -11,7 +11,9 @@ Interfaces
 Norm          load(gamma); forward(x_f32[rows,H] , out[rows,H], row_index=None)
 Position      fused_rotary_table() -> [positions, head_dim/2, 2] float32 or None;
               apply(x[T, heads*head_dim], heads, head_dim, positions) in place (only if no table)
-Mixer         cache_spec() -> KVSpec | StateSpec | None
+Mixer         cache_spec() -> KVSpec | StateSpec | None, or a tuple of one KVSpec and one StateSpec
+Connection    how a sublayer reads its input from several residual streams and puts its output back:
+              read(residual_f32[T, S*H], norm, out[T,H], clear=None); write(residual_f32[T, S*H], y_f32[T,H])
               forward(x[T,H], residual_f32[T,H], ctx, cache_view, writes_cache): adds its output into residual
 FeedForward   forward(x[T,H], residual_f32[T,H], ctx): adds its output into residual
 Transform     forward(t, ctx): changes a whole tensor of the model in place: the residual stream after the
@@ -42,10 +44,23 @@ import torch
 @dataclass(frozen=True)
 class KVSpec:
     """Keys and values per token.  window = 0 keeps every key; window = w keeps
-    the last w keys (the query's own position included)."""
+    the last w keys (the query's own position included), and besides them the
+    first `keep_first` keys of the sequence.  Values may differ from keys in
+    their number of heads and their size (0: as the keys)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    keep_first: int = 0
+    n_value_heads: int = 0
+    value_dim: int = 0
+
+    @property
+    def v_heads(self) -> int:
+        return self.n_value_heads or self.n_kv_heads
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -54,7 +69,20 @@ class StateSpec:
     shape: Tuple[int, ...]
 
 
-CacheSpec = Union[KVSpec, StateSpec, None]
+CacheSpec = Union[KVSpec, StateSpec, Tuple[Union[KVSpec, StateSpec], ...], None]
+
+
+def split_cache_spec(spec: CacheSpec) -> Tuple[Optional[KVSpec], Optional[StateSpec]]:
+    """(keys and values, state) that a place asks for; either may be None.  A mixer may need both
+    (attention whose projections pass a short convolution keeps the last projected values)."""
+    if spec is None:
+        return None, None
+    items = spec if isinstance(spec, tuple) else (spec,)
+    kv = [s for s in items if isinstance(s, KVSpec)]
+    st = [s for s in items if isinstance(s, StateSpec)]
+    if len(kv) + len(st) != len(items) or len(kv) > 1 or len(st) > 1:
+        raise TypeError(f"a cache spec is a KVSpec, a StateSpec or one of each, got {spec!r}")
+    return (kv[0] if kv else None), (st[0] if st else None)
 
 
 # --------------------------------------------------------------------------
@@ -122,6 +150,9 @@ class ModelSpec:
     # after the head, in order; none in the Llama decoder
     embedding_transforms: Tuple[PartSpec, ...] = ()
     logit_transforms: Tuple[PartSpec, ...] = ()
+    # copies of the residual stream per token (hyper-connections): the residual tensor of a step is
+    # [T, residual_streams * hidden_size], every copy starts as the embedding, and the final norm reads their sum
+    residual_streams: int = 1
 
 
 # --------------------------------------------------------------------------
@@ -129,12 +160,13 @@ class ModelSpec:
 # --------------------------------------------------------------------------
 _REGISTRIES: Dict[str, Dict[str, Callable[..., Any]]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "arrangement": {}, "transform": {},
+    "connection": {},
 }
 
 
 def register_part(family: str, kind: str, factory: Callable[..., Any]) -> None:
     """`factory(**params, dtype=..., device=...)` builds the part.  `family` is
-    one of mixer, feed_forward, norm, position, transform; an arrangement's
+    one of mixer, feed_forward, norm, position, transform, connection; an arrangement's
     factory takes `(parts, hidden_size, dtype)`."""
     if family not in _REGISTRIES:
         raise KeyError(f"unknown family '{family}' (have {sorted(_REGISTRIES)})")
@@ -190,6 +222,13 @@ class Norm(Part):
         arrangement passes it when that part asks for it)."""
         raise NotImplementedError
 
+    def forward_streams(self, x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], out: torch.Tensor,
+                        row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+        """The norm of sum_s weights[s] * x[:, s] for x float32 [rows, streams * width] (weights None: the plain
+        sum); `clear`: a float32 [rows, width] tensor set to zero by the same launch.  Needed only by models with
+        several residual streams."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     def fused_rotary_table(self) -> Optional[torch.Tensor]:
@@ -209,6 +248,16 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        raise NotImplementedError
+
+
+class Connection(Part):
+    """How a sublayer meets a residual of several streams."""
+
+    def read(self, residual: torch.Tensor, norm: "Norm", out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+    def write(self, residual: torch.Tensor, y: torch.Tensor) -> None:
         raise NotImplementedError
 
 

@@ -43,3 +43,43 @@ class PreNormBlock:
 
 
 register_part("arrangement", "pre_norm", PreNormBlock)
+
+
+class HyperConnectedBlock:
+    """Pre-norm with several residual streams: each sublayer reads the normed weighted sum of the
+    streams through its connection and its output is mixed back into every stream
+    (`parts.connection`).  `parts`: mixer_norm, mixer, mixer_connection, and, unless the layer has
+    no feed-forward, feed_forward_norm, feed_forward, feed_forward_connection.  The residual of a
+    step is float32 [T, streams * hidden_size]; a sublayer adds its output into a zeroed float32
+    [T, hidden_size] buffer, as it would into a single residual stream."""
+
+    def __init__(self, parts: dict, hidden_size: int, dtype: torch.dtype):
+        unknown = set(parts) - {"mixer_norm", "mixer", "mixer_connection", "feed_forward_norm", "feed_forward",
+                                "feed_forward_connection"}
+        if unknown:
+            raise ValueError(f"the hyper_pre_norm arrangement has no use for the parts {sorted(unknown)}")
+        try:
+            self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
+            self.mixer_connection = parts["mixer_connection"]
+            self.feed_forward = parts.get("feed_forward")
+            self.feed_forward_norm = parts["feed_forward_norm"] if self.feed_forward is not None else None
+            self.feed_forward_connection = parts["feed_forward_connection"] if self.feed_forward is not None else None
+        except KeyError as e:
+            raise ValueError(f"the hyper_pre_norm arrangement needs the part {e.args[0]!r}") from None
+        self.hidden_size, self.dtype = hidden_size, dtype
+
+    def forward(self, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+        T = residual.shape[0]
+        x = ctx.workspace.get("normed", (T, self.hidden_size), self.dtype)
+        y = ctx.workspace.get("sublayer_out", (T, self.hidden_size), torch.float32)
+        self.mixer_connection.read(residual, self.mixer_norm, x, clear=y)
+        self.mixer.forward(x, y, ctx, cache_view, writes_cache)
+        self.mixer_connection.write(residual, y)
+        if self.feed_forward is None:
+            return
+        self.feed_forward_connection.read(residual, self.feed_forward_norm, x, clear=y)
+        self.feed_forward.forward(x, y, ctx)
+        self.feed_forward_connection.write(residual, y)
+
+
+register_part("arrangement", "hyper_pre_norm", HyperConnectedBlock)

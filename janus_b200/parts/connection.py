@@ -1,0 +1,50 @@
+"""Hyper-connections: a layer keeps S copies x_1 .. x_S of the residual stream per token
+instead of one.  A sublayer reads u = sum_s a[s] x_s (normed before it enters the sublayer)
+and, once it has produced y, every stream is rewritten from the old ones at once:
+x_t <- sum_s M[s, t] x_s + b[t] y, with M indexed [from, to].  With S = 1, a = b = M = 1 this is the
+plain residual sum.  The weights a, b, M are float32 on the device whatever the engine dtype;
+the sums are made in float32.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .base import Connection, register_part
+
+
+class HyperConnection(Connection):
+    def __init__(self, streams: int, width: int, dtype: torch.dtype = torch.float32,
+                 device: torch.device = torch.device("cuda")):
+        if streams < 1:
+            raise ValueError(f"a connection needs at least one stream, got {streams}")
+        self.streams, self.width = int(streams), int(width)
+        self.dtype, self.device = dtype, device
+        self.a: Optional[torch.Tensor] = None
+        self.b: Optional[torch.Tensor] = None
+        self.mix: Optional[torch.Tensor] = None
+
+    def weight_shapes(self):
+        return {"into": ((self.streams,), "ones"), "out": ((self.streams,), "ones"),
+                "mix": ((self.streams, self.streams), "eye")}
+
+    def load(self, into: torch.Tensor, out: torch.Tensor, mix: torch.Tensor) -> None:
+        S = self.streams
+        for name, t, shape in (("into", into, (S,)), ("out", out, (S,)), ("mix", mix, (S, S))):
+            if tuple(t.shape) != shape:
+                raise ValueError(f"connection weight '{name}' of shape {tuple(t.shape)} does not fit {shape}")
+        self.a = into.to(device=self.device, dtype=torch.float32).contiguous()
+        self.b = out.to(device=self.device, dtype=torch.float32).contiguous()
+        self.mix = mix.to(device=self.device, dtype=torch.float32).contiguous()
+
+    def read(self, residual: torch.Tensor, norm, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> None:
+        """out = norm(sum_s a[s] x_s); `clear` ([T, width] float32, the sublayer's target) is zeroed on the way."""
+        norm.forward_streams(residual, self.streams, self.a, out, clear=clear)
+
+    def write(self, residual: torch.Tensor, y: torch.Tensor) -> None:
+        ops.streams_mix(residual, y, self.mix, self.b, self.streams)
+
+
+register_part("connection", "hyper_connection", HyperConnection)

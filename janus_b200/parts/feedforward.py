@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import ops
 from .base import FeedForward, register_part
 from .linear import GatedLinear, Linear
 
@@ -32,4 +33,36 @@ class SwiGLUFeedForward(FeedForward):
         self.down.forward_add(act, residual)
 
 
+class ClampedGLUFeedForward(FeedForward):
+    """down( g * sigmoid(alpha g) * (u + 1) ) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit),
+    added into the residual stream.  Gate and up run as one product of the stacked rows into float32; the
+    activation reads the accumulators."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
+                 dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.dtype, self.device = dtype, device
+        self.gate_up = Linear(hidden_size, 2 * intermediate_size, dtype, device, name="gate_up")
+        self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down")
+
+    def weight_shapes(self):
+        return {"gate": ((self.intermediate_size, self.hidden_size), "normal"),
+                "up": ((self.intermediate_size, self.hidden_size), "normal"),
+                "down": ((self.hidden_size, self.intermediate_size), "normal")}
+
+    def load(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> None:
+        self.gate_up.load([gate, up])
+        self.down.load([down])
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        T, I = x.shape[0], self.intermediate_size
+        gu = ctx.workspace.get("gate_up", (T, 2 * I), torch.float32)
+        self.gate_up.forward(x, gu)
+        act = ctx.workspace.get("ffn_act", (T, I), self.dtype)
+        ops.clamped_glu(gu, act, I, self.limit, self.alpha)
+        self.down.forward_add(act, residual)
+
+
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+register_part("feed_forward", "clamped_glu", ClampedGLUFeedForward)

@@ -33,5 +33,10 @@ class RMSNorm(Norm):
         """`clear`: a float32 scratch tensor of the part that runs next, set to zero by the same launch."""
         ops.rmsnorm(x, self.gamma, self.eps, out, row_index, clear)
 
+    def forward_streams(self, x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], out: torch.Tensor,
+                        row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+        """The norm of the weighted sum of `streams` residual streams, summed and normed in one launch."""
+        ops.streams_rmsnorm(x, streams, weights, self.gamma, self.eps, out, row_index, clear)
+
 
 register_part("norm", "rms_norm", RMSNorm)

@@ -72,6 +72,51 @@ class RotaryEncoding(PositionEncoding):
         return self.table
 
 
+def ramped_scaled(inv_freq: torch.Tensor, dims: int, base: float, factor: float, original: float, fast: float,
+                  slow: float):
+    """Frequencies blended between their own value and value / factor by a linear ramp over the pair index
+    (YaRN-style): with pair(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(pair(fast)), 0),
+    hi = min(ceil(pair(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+    f_i / factor * ramp_i + f_i * (1 - ramp_i).  Returns (frequencies, the factor 0.1 ln(factor) + 1 that cos and
+    sin are multiplied by)."""
+    def pair(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair(fast)), 0)
+    hi = min(math.ceil(pair(slow)), dims - 1)
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    f = inv_freq.to(torch.float64)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class RampedRotaryEncoding(RotaryEncoding):
+    """Rotary positions on the first `dims` dimensions of a vector (the mixer passes the rest through), the
+    frequencies scaled by `ramped_scaled` when `scaling` (factor, original, fast, slow) is given; cos and sin
+    carry the scaling's amplitude factor.  The table is made on the host in float64 (frequencies, angles
+    position * frequency, cos and sin) and rounded to float32 once."""
+
+    def __init__(self, dims: int, theta: float, max_positions: int, scaling: Optional[dict] = None,
+                 dtype: torch.dtype = torch.float32, device: torch.device = torch.device("cpu")):
+        super().__init__(dims, theta, max_positions, None, dtype, device)
+        self.dims = int(dims)
+        self.amplitude = 1.0
+        exponent = torch.arange(0, dims, 2, dtype=torch.float64) / float(dims)
+        self.inv_freq = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -exponent)
+        if scaling is not None:
+            self.inv_freq, self.amplitude = ramped_scaled(
+                self.inv_freq, self.dims, float(theta), float(scaling["factor"]), float(scaling["original"]),
+                float(scaling["fast"]), float(scaling["slow"]))
+
+    @property
+    def table(self) -> torch.Tensor:
+        if self._table is None:
+            angle = torch.arange(self._limit, dtype=torch.float64)[:, None] * self.inv_freq.to(torch.float64)[None, :]
+            self._table = (torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1) * self.amplitude) \
+                .to(torch.float32).contiguous().to(self.device)
+        return self._table
+
+
 class NoPositions(PositionEncoding):
     """A mixer whose order information comes from elsewhere."""
 
@@ -83,4 +128,5 @@ class NoPositions(PositionEncoding):
 
 
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "ramped_rotary", RampedRotaryEncoding)
 register_part("position", "none", NoPositions)

@@ -34,7 +34,7 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class TensorSpec:
     """What a model expects of one tensor.  `init` tells the random source how
-    to fill it: "normal" (N(0, std)) or "ones" (1 + N(0, norm_std))."""
+    to fill it: "normal" (N(0, std)), "ones" (1 + N(0, norm_std)) or "eye" (identity + N(0, norm_std))."""
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"

@@ -8,7 +8,8 @@ on the order of creation, or on the device that evaluates the function.  It uses
 64-bit integer arithmetic and exact float operations only (no logarithm, no
 cosine), so the host and the device give the same bits: a model made on the GPU
 can be made again on the CPU for an oracle.
-Matrices and embeddings are ~N(0, std); norm weights are 1 + ~N(0, norm_std).
+Matrices and embeddings are ~N(0, std); norm weights are 1 + ~N(0, norm_std); a
+matrix that mixes streams ("eye") is the identity + ~N(0, norm_std).
 The normal variate is the sum of twelve uniform 16-bit integers, centred and
 scaled to variance one (Irwin-Hall: tails end at six standard deviations).
 """
@@ -108,6 +109,10 @@ class RandomCheckpoint:
             z = standard_normal(key, start, min(_CHUNK, n - start), self.device)
             if spec.init == "ones":
                 z = z * self.norm_std + 1.0
+            elif spec.init == "eye":
+                # a square matrix near the identity: 1 + noise on the diagonal, noise off it
+                i = torch.arange(start, start + z.numel(), device=self.device)
+                z = z * self.norm_std + (i // spec.shape[-1] == i % spec.shape[-1]).to(torch.float32)
             else:
                 z = z * self.std
             out[start:start + z.numel()] = z.to(self._dtype)
