@@ -644,6 +644,96 @@ def run_kernels(contexts=None, shape="8b", head_sizes=None):
     ops.check_kernel_status(torch.device(dev))
 
 
+DESIGN_SIZES = {
+    # name: width, feed-forward, heads, key/value heads, window; four layers each: one lightning mixer, three
+    # differential attention mixers (key size 64 per map, value size 128), two residual streams
+    "2k": dict(width=2048, ff=8192, heads=16, kv_heads=4, window=1024, vocab=32000),
+    "4k": dict(width=4096, ff=14336, heads=32, kv_heads=8, window=2048, vocab=32000),
+}
+
+
+def zivitar_config(width, ff, heads, kv_heads, window, vocab):
+    attention = dict(type="attention", mlp=dict(kind="dense", ff=ff, limit=7.0),
+                     mixer=dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=128, scale=0.125, diff=0.5, conv=4,
+                                mask=dict(size=window, keep_first=4),
+                                rot=dict(dims=32, base=10000.0, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0))))
+    lightning = dict(type="lightning", mlp=dict(kind="dense", ff=ff, limit=7.0),
+                     mixer=dict(heads=heads, dim=128, vdim=128, decay=[1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)]))
+    return dict(architecture="Zivitar", vocab=vocab, width=width, norm=dict(eps=1e-5), streams=2, logit_scale=1.0,
+                logit_softcap=30.0, layers=[lightning, attention, attention, attention])
+
+
+def llama_like(width, ff, heads, kv_heads, window, vocab):
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=width, num_hidden_layers=4, num_attention_heads=heads,
+                num_key_value_heads=kv_heads, head_dim=128, intermediate_size=ff, vocab_size=vocab,
+                max_position_embeddings=16384, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+                tie_word_embeddings=False)
+
+
+def run_design(which):
+    """The Zivitar design beside the Llama decoder at equal layer sizes (random weights, four layers): prompt
+    steps and decode steps timed on the device, and each step's kernels one by one (`Model.profile`).  One
+    JSON line per (size, model)."""
+    import torch
+
+    import janus_b200
+    from janus_b200.engine.step import StepEntry
+    for name in which.split(","):
+        size = DESIGN_SIZES[name]
+        for label, cfg in (("zivitar", zivitar_config(**size)), ("llama", llama_like(**size))):
+            model = janus_b200.load_random(cfg, seed=5, dtype="bfloat16", max_tokens=8 * 2176 + 8192 + 1024, max_slots=16,
+                                           max_seq_len=16384, norm_std=0.0)
+            V = size["vocab"]
+            g = torch.Generator().manual_seed(1)
+
+            def toks(n):
+                return torch.randint(0, V, (n,), generator=g).tolist()
+
+            def timed(fn, reps):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) / reps
+
+            out = {"impl": "janus_b200", "design": label, "size": name, "layers": 4, "dtype": "bf16",
+                   "data": "synthetic token ids, random-init weights (seed 5)", "config": size}
+            for n in (2048, 8192):
+                prompt = toks(n)
+
+                def prefill():
+                    s = model.alloc_slot()
+                    model.step([StepEntry(s, prompt, (n - 1,))])
+                    model.free_slot(s)
+                ms = timed(prefill, 4)
+                out[f"prefill_{n}_ms"] = round(ms, 3)
+                out[f"prefill_{n}_tokens_per_s"] = round(n / ms * 1e3, 0)
+            slots = [model.alloc_slot() for _ in range(8)]
+            model.step([StepEntry(s, toks(2048), ()) for s in slots])
+            tok = toks(8)
+
+            def decode():
+                model.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, tok)])
+            ms = timed(decode, 32)
+            out["decode_batch8_ctx2048_ms"] = round(ms, 4)
+            out["decode_batch8_ctx2048_tokens_per_s"] = round(8 / ms * 1e3, 0)
+            for s in slots:
+                model.free_slot(s)
+            prof = model.profile([toks(2048)])
+            out["prefill_2048_kernels"] = {k["name"]: [k["launches"], k["ms"]] for k in prof["prefill"]["kernels"]}
+            prof = model.profile([toks(2048) for _ in range(8)])
+            out["decode_batch8_kernels"] = {k["name"]: [k["launches"], k["ms"]] for k in prof["decode"]["kernels"]}
+            model.check()
+            print(json.dumps(out), flush=True)
+            del model
+            torch.cuda.empty_cache()
+
+
 def run_plan_check():
     """The pick of `ops.gemm_plan` against every alternative it ranks (single-CTA kernel and CTA pairs, K in
     1 to 8 slices) for adding products of three layer sizes at decode and prompt token counts: each variant
@@ -795,6 +885,9 @@ def main():
     ap.add_argument("--cpu-baseline", action="store_true",
                     help="time the plain implementation of tests/ on the host (the only runnable stand-in for the "
                          "reference on this box): Tiny A, Tiny B and one 8B-sized layer (one JSON line each)")
+    ap.add_argument("--design", nargs="?", const="2k,4k", default=None, metavar="SIZE,...",
+                    help="the Zivitar design beside the Llama decoder at equal layer sizes (" + ", ".join(DESIGN_SIZES) +
+                         "): prompt and decode throughput and each step's kernels, one JSON line per size and model")
     args = ap.parse_args()
     if args.cpu_baseline:
         run_cpu_baseline()
@@ -818,6 +911,9 @@ def main():
         return 0
     if args.plan_check:
         run_plan_check()
+        return 0
+    if args.design:
+        run_design(args.design)
         return 0
     if args.prompt_lengths:
         run_prompt_lengths(args.layers or 8, args.prompt_lengths)

@@ -14,11 +14,12 @@
 //                     (i, i + rot/2), cos and sin from a table); q goes out in float32, k and v
 //                     into the cache.
 //   conv_state_update: the state takes the step's last projected values.
-//   diff_attention:   one warp per (token, query head); both maps' online softmax over the visible
+//   diff_attention:   one block per (token, query head); both maps' online softmax over the visible
 //                     keys j <= i with (i - j < window or j < keep_first), in chunks of 32 keys that
-//                     start at multiples of 32 of the key index (so the result does not depend on how
-//                     a sequence was cut into steps); o = a1 - lambda a2, divided by its root mean
-//                     square over the head's e values (eps inside the root), times out_scale.
+//                     start at multiples of 32 of the key index and go to the block's warps in turn (so
+//                     the result does not depend on how a sequence was cut into steps); o = a1 - lambda a2,
+//                     divided by its root mean square over the head's e values (eps inside the root),
+//                     times out_scale.  It serves single tokens in both dtypes and every float32 step.
 // Scores, softmax weights and the sums are float32 whatever the cache holds.
 #include <math_constants.h>
 #include <stdio.h>
@@ -103,29 +104,81 @@ __global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld,
   }
 }
 
-constexpr int WARPS = 4;
+constexpr int MAX_WARPS = 8;
 
+// dot products of one key's two maps with the query's two maps, 8 (bf16) or 4 (float) elements a load when
+// the rows allow it
+template <typename TC>
+__device__ __forceinline__ void dot2(const float* __restrict__ qw, const TC* __restrict__ k1, const TC* __restrict__ k2,
+                                     int d, bool vec, float& d1, float& d2);
+
+template <>
+__device__ __forceinline__ void dot2<float>(const float* __restrict__ qw, const float* __restrict__ k1,
+                                            const float* __restrict__ k2, int d, bool vec, float& d1, float& d2) {
+  d1 = d2 = 0.0f;
+  if (vec) {
+    for (int i = 0; i < d; i += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(k1 + i), b = *reinterpret_cast<const float4*>(k2 + i);
+      d1 = fmaf(qw[i], a.x, d1); d1 = fmaf(qw[i + 1], a.y, d1); d1 = fmaf(qw[i + 2], a.z, d1); d1 = fmaf(qw[i + 3], a.w, d1);
+      d2 = fmaf(qw[d + i], b.x, d2); d2 = fmaf(qw[d + i + 1], b.y, d2); d2 = fmaf(qw[d + i + 2], b.z, d2);
+      d2 = fmaf(qw[d + i + 3], b.w, d2);
+    }
+  } else {
+    for (int i = 0; i < d; ++i) {
+      d1 = fmaf(qw[i], k1[i], d1);
+      d2 = fmaf(qw[d + i], k2[i], d2);
+    }
+  }
+}
+
+template <>
+__device__ __forceinline__ void dot2<bf16>(const float* __restrict__ qw, const bf16* __restrict__ k1,
+                                           const bf16* __restrict__ k2, int d, bool vec, float& d1, float& d2) {
+  d1 = d2 = 0.0f;
+  if (vec) {
+#pragma unroll 4
+    for (int i = 0; i < d; i += 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(k1 + i), b = *reinterpret_cast<const uint4*>(k2 + i);
+      const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 af = __bfloat1622float2(ap[u]), bf = __bfloat1622float2(bp[u]);
+        d1 = fmaf(qw[i + 2 * u], af.x, d1);
+        d1 = fmaf(qw[i + 2 * u + 1], af.y, d1);
+        d2 = fmaf(qw[d + i + 2 * u], bf.x, d2);
+        d2 = fmaf(qw[d + i + 2 * u + 1], bf.y, d2);
+      }
+    }
+  } else {
+    for (int i = 0; i < d; ++i) {
+      d1 = fmaf(qw[i], __bfloat162float(k1[i]), d1);
+      d2 = fmaf(qw[d + i], __bfloat162float(k2[i]), d2);
+    }
+  }
+}
+
+// One block per (token, query head); its warps take the chunks of 32 keys in turn (chunk n goes to warp
+// n mod warps) and their partial results (maximum, sum, weighted values of each map) meet in warp order.
 // EJ: value columns a lane holds (e <= 32 EJ)
 template <typename TC, typename TO, int EJ>
-__global__ void __launch_bounds__(WARPS * 32) diff_attention_kernel(
+__global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
     const float* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, TO* __restrict__ out,
     const int* __restrict__ block_table, const int* __restrict__ token_seq, const int* __restrict__ positions, int T, int H,
     int G, int d, int e, int page_size, int max_pages, int window, int keep_first, float scale, float lambda, float eps,
-    float out_scale) {
-  extern __shared__ float q_s[];                     // [WARPS][2 d]
+    float out_scale, int vec) {
+  extern __shared__ float smem[];                    // q [2 d], then per warp: m1 l1 m2 l2, a1 [32 EJ], a2 [32 EJ]
   jb::pdl_launch_dependents();
   jb::pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * WARPS + warp;
-  if (item >= (long long)T * H) return;
-  const int t = (int)(item / H), h = (int)(item % H);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x / H, h = blockIdx.x % H;
   const int g = h / (H / G);
   const int pos = positions[t];
   const int* pages = block_table + (size_t)token_seq[t] * max_pages;
   const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  float* qw = q_s + warp * 2 * d;
-  for (int i = lane; i < 2 * d; i += 32) qw[i] = q[((size_t)t * H + h) * 2 * d + i];
-  __syncwarp();
+  float* qw = smem;
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) qw[i] = q[((size_t)t * H + h) * 2 * d + i];
+  __syncthreads();
 
   float m1 = -CUDART_INF_F, l1 = 0.0f, m2 = -CUDART_INF_F, l2 = 0.0f;
   float a1[EJ], a2[EJ];
@@ -139,12 +192,8 @@ __global__ void __launch_bounds__(WARPS * 32) diff_attention_kernel(
     if (valid) {
       const int page = pages[key / page_size], row = key % page_size;
       const TC* k1 = k_cache + (((size_t)page * 2 * G + 2 * g) * page_size + row) * d;
-      const TC* k2 = k1 + (size_t)page_size * d;
-      float d1 = 0.0f, d2 = 0.0f;
-      for (int i = 0; i < d; ++i) {
-        d1 = fmaf(qw[i], jb::to_f32(k1[i]), d1);
-        d2 = fmaf(qw[d + i], jb::to_f32(k2[i]), d2);
-      }
+      float d1, d2;
+      dot2<TC>(qw, k1, k1 + (size_t)page_size * d, d, vec != 0, d1, d2);
       s1 = d1 * scale;
       s2 = d2 * scale;
     }
@@ -160,19 +209,48 @@ __global__ void __launch_bounds__(WARPS * 32) diff_attention_kernel(
       a2[j] *= c2;
     }
     const unsigned seen = __ballot_sync(0xffffffffu, valid);
-    for (int kk = 0; kk < 32; ++kk) {
-      if (!((seen >> kk) & 1u)) continue;            // uniform across the warp
-      const int key2 = c0 + kk;
-      const int page = pages[key2 / page_size], row = key2 % page_size;
-      const TC* vr = v_cache + (((size_t)page * G + g) * page_size + row) * e;
-      const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
+    if (page_size % 32 == 0) {
+      // the chunk lies in one page, which is held because the chunk has a visible key: eight value rows are
+      // loaded before their products are added, in key order (keys that are not seen carry the weight zero)
+      const int page = pages[c0 / page_size];
+      const TC* vbase = v_cache + (((size_t)page * G + g) * page_size + c0 % page_size) * e;
+      const int kk_lo = __ffs(seen) - 1, kk_hi = 32 - __clz(seen);
+      for (int kk0 = kk_lo & ~7; kk0 < kk_hi; kk0 += 8) {
+        float vreg[8][EJ];
 #pragma unroll
-      for (int j = 0; j < EJ; ++j) {
-        const int c = lane + 32 * j;
-        if (c < e) {
-          const float v = jb::to_f32(vr[c]);
-          a1[j] = fmaf(w1, v, a1[j]);
-          a2[j] = fmaf(w2, v, a2[j]);
+        for (int u = 0; u < 8; ++u) {
+          const TC* vr = vbase + (size_t)(kk0 + u) * e;
+#pragma unroll
+          for (int j = 0; j < EJ; ++j) {
+            const int c = lane + 32 * j;
+            vreg[u][j] = c < e ? jb::to_f32(vr[c]) : 0.0f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float w1 = __shfl_sync(0xffffffffu, p1, kk0 + u), w2 = __shfl_sync(0xffffffffu, p2, kk0 + u);
+#pragma unroll
+          for (int j = 0; j < EJ; ++j) {
+            a1[j] = fmaf(w1, vreg[u][j], a1[j]);
+            a2[j] = fmaf(w2, vreg[u][j], a2[j]);
+          }
+        }
+      }
+    } else {
+      for (int kk = 0; kk < 32; ++kk) {
+        if (!((seen >> kk) & 1u)) continue;            // uniform across the warp
+        const int key2 = c0 + kk;
+        const int page = pages[key2 / page_size], row = key2 % page_size;
+        const TC* vr = v_cache + (((size_t)page * G + g) * page_size + row) * e;
+        const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
+#pragma unroll
+        for (int j = 0; j < EJ; ++j) {
+          const int c = lane + 32 * j;
+          if (c < e) {
+            const float v = jb::to_f32(vr[c]);
+            a1[j] = fmaf(w1, v, a1[j]);
+            a2[j] = fmaf(w2, v, a2[j]);
+          }
         }
       }
     }
@@ -180,11 +258,41 @@ __global__ void __launch_bounds__(WARPS * 32) diff_attention_kernel(
     m2 = n2;
   };
 
+  // chunks are numbered by their place in the key index, so a key is always handled by the same warp of its
+  // query's block and in the same order, however the sequence was cut into steps
   const int first_window_chunk = (kstart / 32) * 32;
   const int kept = min(keep_first, kstart);          // kept keys that the window has left behind
-  for (int c0 = 0; c0 < kept && c0 < first_window_chunk; c0 += 32) chunk(c0);
-  for (int c0 = first_window_chunk; c0 <= pos; c0 += 32) chunk(c0);
+  for (int c0 = 32 * warp; c0 < kept && c0 < first_window_chunk; c0 += 32 * warps) chunk(c0);
+  for (int c0 = first_window_chunk + 32 * warp; c0 <= pos; c0 += 32 * warps) chunk(c0);
 
+  // the warps' parts meet in warp order in warp 0
+  float* part = smem + 2 * d + (size_t)warp * (4 + 64 * EJ);
+  if (lane == 0) {
+    part[0] = m1; part[1] = l1; part[2] = m2; part[3] = l2;
+  }
+#pragma unroll
+  for (int j = 0; j < EJ; ++j) {
+    part[4 + 32 * j + lane] = a1[j];
+    part[4 + 32 * EJ + 32 * j + lane] = a2[j];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  for (int w = 1; w < warps; ++w) {
+    const float* pw = smem + 2 * d + (size_t)w * (4 + 64 * EJ);
+    const float om1 = pw[0], ol1 = pw[1], om2 = pw[2], ol2 = pw[3];
+    if (om1 == -CUDART_INF_F) continue;              // that warp saw no key
+    const float n1 = fmaxf(m1, om1), n2 = fmaxf(m2, om2);
+    const float c1 = expf(m1 - n1), e1 = expf(om1 - n1), c2 = expf(m2 - n2), e2 = expf(om2 - n2);
+    l1 = l1 * c1 + ol1 * e1;
+    l2 = l2 * c2 + ol2 * e2;
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) {
+      a1[j] = a1[j] * c1 + pw[4 + 32 * j + lane] * e1;
+      a2[j] = a2[j] * c2 + pw[4 + 32 * EJ + 32 * j + lane] * e2;
+    }
+    m1 = n1;
+    m2 = n2;
+  }
   float o[EJ], ss = 0.0f;
 #pragma unroll
   for (int j = 0; j < EJ; ++j) {
@@ -241,14 +349,19 @@ JB_EXPORT int jb_diff_attention(const float* q, const void* k_cache, const void*
   if (T <= 0) return 0;
   JB_REFUSE(G <= 0 || H % G != 0, "diff_attention: %d heads are not a multiple of %d key/value heads", H, G);
   JB_REFUSE(e < 1 || e > 256 || d < 1 || d > 1024, "diff_attention: sizes %d (keys) and %d (values) are not supported", d, e);
-  const long long items = (long long)T * H;
-  const size_t smem = (size_t)WARPS * 2 * d * sizeof(float);
-  jb::Launch cfg(dim3((unsigned)((items + WARPS - 1) / WARPS)), dim3(WARPS * 32), smem, stream);
+  JB_REFUSE((long long)T * H > 2147483647LL, "diff_attention: %d tokens of %d heads are too many blocks", T, H);
+  // few (token, head) pairs (single tokens): eight warps share a query's keys; prompts: four
+  const int warps = (long long)T * H <= 4096 ? MAX_WARPS : 4;
+  const int EJ_ = e <= 64 ? 2 : e <= 128 ? 4 : 8;
+  const size_t smem = (size_t)(2 * d + warps * (4 + 64 * EJ_)) * sizeof(float);
+  const bool f32c = cache_dtype == JB_F32;
+  const int vec = (d % (f32c ? 4 : 8) == 0) && (((uintptr_t)k_cache) & 15) == 0 ? 1 : 0;
+  jb::Launch cfg(dim3((unsigned)(T * H)), dim3(warps * 32), smem, stream);
   cudaError_t err;
 #define JB_LAUNCH_DA(TC, TO, EJ)                                                                                     \
   err = cudaLaunchKernelEx(&cfg.c, diff_attention_kernel<TC, TO, EJ>, q, (const TC*)k_cache, (const TC*)v_cache,     \
                            (TO*)out, block_table, token_seq, positions, T, H, G, d, e, page_size, max_pages, window, \
-                           keep_first, scale, lambda, eps, out_scale)
+                           keep_first, scale, lambda, eps, out_scale, vec)
 #define JB_LAUNCH_DA_E(TC, TO)            \
   do {                                    \
     if (e <= 64) JB_LAUNCH_DA(TC, TO, 2); \

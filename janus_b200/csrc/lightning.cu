@@ -6,11 +6,17 @@
 //   with q = silu(.), k = silu(.), v = silu(.) of the projection's float32 output.
 //
 // lightning_scan: a block owns one (sequence, head, block of EB value columns); a thread owns
-// one value column and every PARTS-th row of S in registers, walks the sequence's new tokens in
-// order (chunks of CT tokens are staged in shared memory, activated on the way), and the PARTS
+// one value column and a quarter of the rows of S in registers, walks the tokens in order
+// (chunks of CT tokens are staged in shared memory, activated on the way), and the four
 // partial sums of o meet by shuffles in a fixed order.  The state is read from and written back
-// to the sequence's slot, so prompts, portions of prompts and single tokens are the same code
-// and give the same bits.
+// to the sequence's slot, so prompts, portions of prompts and single tokens are the same code.
+//
+// Long prompts run in segments of `seg_len` tokens so that the segments of one sequence run side
+// by side: (1) every segment but a sequence's last computes the state it would reach from zero,
+// (2) a prefix pass turns these into every segment's starting state,
+//     start_(s+1) = lambda^seg_len start_s + local_s, in float32, one thread per element,
+// (3) every segment walks its tokens again from its starting state and writes the outputs; the
+//     last one leaves the sequence's state.  The recurrence itself is the same code in all cases.
 //
 // gated_rmsnorm: out = o / sqrt(mean(o^2) + eps) * w * sigmoid(g), one block per token, over
 // the concatenated heads.
@@ -22,73 +28,119 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int PARTS = 4;      // threads that share a value column (rows r = part, part + 4, ...)
+constexpr int PARTS = 4;      // threads that share a value column (each a quarter of the rows)
 constexpr int EB = 32;        // value columns a block owns
 constexpr int CT = 16;        // tokens staged at a time
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
-// RMAX: rows of S a thread holds at most (ceil(d / PARTS) <= RMAX)
+enum { WHOLE = 0, LOCAL = 1, FROM_START = 3 };
+
+// RMAX: rows of S a thread holds (a multiple of 4, 4 RMAX >= d); shared rows are padded to 4 RMAX with zeros
 template <int RMAX>
 __global__ void __launch_bounds__(EB * PARTS) lightning_scan_kernel(
     const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, float* __restrict__ out,
     float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ seq_slot,
-    const float* __restrict__ decay, int H, int d, int e) {
-  extern __shared__ float smem[];          // q [CT][d], k [CT][d], v [CT][EB]
+    const float* __restrict__ decay, int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch,
+    int phase) {
+  constexpr int DP = PARTS * RMAX;         // padded rows
+  extern __shared__ __align__(16) float smem[];          // q [CT][DP], k [CT][DP], v [CT][EB]
   float* q_s = smem;
-  float* k_s = q_s + CT * d;
-  float* v_s = k_s + CT * d;
+  float* k_s = q_s + CT * DP;
+  float* v_s = k_s + CT * DP;
   jb::pdl_launch_dependents();
-  const int seq = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * EB;
+  const int seq = blockIdx.x / tiles_per_seq, seg = blockIdx.x % tiles_per_seq;
+  const int h = blockIdx.y, e0 = blockIdx.z * EB;
   const int part = threadIdx.x % PARTS, col = threadIdx.x / PARTS;
   const int j = e0 + col;
   const float lam = decay[h];
   jb::pdl_wait();
-  const int t0 = q_start[seq], t1 = q_start[seq + 1];
+  const int s0 = q_start[seq], q_len = q_start[seq + 1] - s0;
+  if ((long long)seg * seg_len >= q_len) return;
+  const int t0 = s0 + seg * seg_len, t1 = min(s0 + q_len, t0 + seg_len);
+  const bool last = t1 == s0 + q_len;
+  if (phase == LOCAL && last) return;              // nobody needs the last segment's state from zero
   float* st = state + (((size_t)seq_slot[seq] * H + h) * d) * e;     // [d][e]
+  float* sc = scratch ? scratch + (((size_t)blockIdx.x * H + h) * d) * e : nullptr;
+  const float* init = phase == WHOLE ? st : phase == FROM_START ? sc : nullptr;
   float S[RMAX];
 #pragma unroll
   for (int i = 0; i < RMAX; ++i) {
-    const int r = part + PARTS * i;
-    S[i] = (r < d && j < e) ? st[(size_t)r * e + j] : 0.0f;
+    const int r = part * RMAX + i;
+    S[i] = (init && r < d && j < e) ? init[(size_t)r * e + j] : 0.0f;
   }
   for (int c0 = t0; c0 < t1; c0 += CT) {
     const int n = min(CT, t1 - c0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
-      const int tt = idx / d, r = idx % d;
+    for (int idx = threadIdx.x; idx < n * DP; idx += blockDim.x) {
+      const int tt = idx / DP, r = idx % DP;
       const float* row = proj + (size_t)(c0 + tt) * ld;
-      q_s[tt * d + r] = silu_f(row[q_col + h * d + r]);
-      k_s[tt * d + r] = silu_f(row[k_col + h * d + r]);
+      q_s[idx] = r < d ? silu_f(row[q_col + h * d + r]) : 0.0f;
+      k_s[idx] = r < d ? silu_f(row[k_col + h * d + r]) : 0.0f;
     }
     for (int idx = threadIdx.x; idx < n * EB; idx += blockDim.x) {
       const int tt = idx / EB, c = idx % EB;
-      v_s[tt * EB + c] = e0 + c < e ? silu_f(proj[(size_t)(c0 + tt) * ld + v_col + h * e + e0 + c]) : 0.0f;
+      v_s[idx] = e0 + c < e ? silu_f(proj[(size_t)(c0 + tt) * ld + v_col + h * e + e0 + c]) : 0.0f;
     }
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float v = v_s[tt * EB + col];
-      const float* qr = q_s + tt * d;
-      const float* kr = k_s + tt * d;
-      float acc = 0.0f;
+      const float4* qr = reinterpret_cast<const float4*>(q_s + tt * DP + part * RMAX);
+      const float4* kr = reinterpret_cast<const float4*>(k_s + tt * DP + part * RMAX);
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-      for (int i = 0; i < RMAX; ++i) {
-        const int r = part + PARTS * i;
-        if (r < d) {
-          S[i] = fmaf(lam, S[i], kr[r] * v);
-          acc = fmaf(S[i], qr[r], acc);
-        }
+      for (int i = 0; i < RMAX / 4; ++i) {
+        const float4 k4 = kr[i], q4 = qr[i];
+        S[4 * i] = fmaf(lam, S[4 * i], k4.x * v);
+        S[4 * i + 1] = fmaf(lam, S[4 * i + 1], k4.y * v);
+        S[4 * i + 2] = fmaf(lam, S[4 * i + 2], k4.z * v);
+        S[4 * i + 3] = fmaf(lam, S[4 * i + 3], k4.w * v);
+        a0 = fmaf(S[4 * i], q4.x, a0);
+        a1 = fmaf(S[4 * i + 1], q4.y, a1);
+        a2 = fmaf(S[4 * i + 2], q4.z, a2);
+        a3 = fmaf(S[4 * i + 3], q4.w, a3);
       }
-      // the four parts of a column are neighbouring lanes: part 0 + 1, 2 + 3, then the two sums
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (part == 0 && j < e) out[(size_t)(c0 + tt) * H * e + (size_t)h * e + j] = acc;
+      if (phase != LOCAL) {
+        float acc = (a0 + a1) + (a2 + a3);
+        // the four parts of a column are neighbouring lanes: part 0 + 1, 2 + 3, then the two sums
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (part == 0 && j < e) out[(size_t)(c0 + tt) * H * e + (size_t)h * e + j] = acc;
+      }
     }
   }
+  float* dst = phase == LOCAL ? sc : (last ? st : nullptr);
+  if (dst == nullptr) return;
 #pragma unroll
   for (int i = 0; i < RMAX; ++i) {
-    const int r = part + PARTS * i;
-    if (r < d && j < e) st[(size_t)r * e + j] = S[i];
+    const int r = part * RMAX + i;
+    if (r < d && j < e) dst[(size_t)r * e + j] = S[i];
+  }
+}
+
+// scratch[seq][seg] holds segment seg's state from zero; afterwards it holds the state the segment starts from
+__global__ void lightning_prefix_kernel(float* __restrict__ scratch, const float* __restrict__ state,
+                                        const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                        const float* __restrict__ decay, int H, int d, int e, int seg_len,
+                                        int tiles_per_seq) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int seq = blockIdx.x;
+  const size_t per = (size_t)H * d * e;
+  const size_t idx = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+  if (idx >= per) return;
+  const int h = (int)(idx / ((size_t)d * e));
+  const int q_len = q_start[seq + 1] - q_start[seq];
+  const int n_seg = (q_len + seg_len - 1) / seg_len;
+  const float lam = decay[h];
+  float lam_seg = 1.0f;
+  for (int i = 0; i < seg_len; ++i) lam_seg *= lam;          // the decay of a whole segment, as the walk applies it
+  float S = state[(size_t)seq_slot[seq] * per + idx];
+  for (int seg = 0; seg < n_seg; ++seg) {
+    float* p = scratch + ((size_t)seq * tiles_per_seq + seg) * per + idx;
+    const float local = seg + 1 < n_seg ? *p : 0.0f;
+    *p = S;
+    S = fmaf(lam_seg, S, local);
   }
 }
 
@@ -115,23 +167,48 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const TG* __re
 
 // proj: float32 [T, ld], the raw projections: q at column q_col ([H][d]), k at k_col ([H][d]), v at v_col ([H][e]);
 // out: float32 [T, H * e]; state: float32 [slots, H, d, e]; q_start: [n_seqs + 1] rows of each sequence's tokens;
-// seq_slot: [n_seqs]; decay: [H] float32.
+// seq_slot: [n_seqs]; decay: [H] float32.  seg_len > 0 with scratch (float32, n_seqs * ceil(max_q_len / seg_len) *
+// H * d * e) runs the three passes over segments; seg_len = 0 walks every sequence in one block per column block.
 JB_EXPORT int jb_lightning_scan(const float* proj, int ld, int q_col, int k_col, int v_col, float* out, float* state,
                                 const int* q_start, const int* seq_slot, const float* decay, int n_seqs, int H, int d,
-                                int e, cudaStream_t stream) {
+                                int e, int max_q_len, int seg_len, float* scratch, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   JB_REFUSE(d < 1 || d > 256 || e < 1, "lightning_scan: key size %d is outside [1, 256]", d);
-  const size_t smem = (size_t)(2 * CT * d + CT * EB) * sizeof(float);
-  jb::Launch cfg(dim3(n_seqs, H, (e + EB - 1) / EB), dim3(EB * PARTS), smem, stream);
-  const int rows = (d + PARTS - 1) / PARTS;
-  if (rows <= 16)
-    return (int)cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<16>, proj, ld, q_col, k_col, v_col, out, state, q_start,
-                                   seq_slot, decay, H, d, e);
-  if (rows <= 32)
-    return (int)cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<32>, proj, ld, q_col, k_col, v_col, out, state, q_start,
-                                   seq_slot, decay, H, d, e);
-  return (int)cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<64>, proj, ld, q_col, k_col, v_col, out, state, q_start,
-                                 seq_slot, decay, H, d, e);
+  JB_REFUSE(seg_len > 0 && scratch == nullptr, "lightning_scan: segments need scratch");
+  const int rmax = d <= 64 ? 16 : d <= 128 ? 32 : 64;
+  const size_t smem = (size_t)(2 * CT * PARTS * rmax + CT * EB) * sizeof(float);
+  const bool segmented = seg_len > 0;
+  const int tiles = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
+  const int seg = segmented ? seg_len : 0x40000000;
+#define JB_LAUNCH_LS(RM, PHASE)                                                                                      \
+  do {                                                                                                               \
+    jb::Launch cfg(dim3(n_seqs * tiles, H, (e + EB - 1) / EB), dim3(EB * PARTS), smem, stream);                     \
+    cudaError_t err = cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<RM>, proj, ld, q_col, k_col, v_col, out,     \
+                                         state, q_start, seq_slot, decay, H, d, e, seg, tiles, scratch, (int)PHASE); \
+    if (err != cudaSuccess) return (int)err;                                                                         \
+  } while (0)
+#define JB_LAUNCH_LS_R(PHASE)                       \
+  do {                                              \
+    if (rmax == 16) JB_LAUNCH_LS(16, PHASE);        \
+    else if (rmax == 32) JB_LAUNCH_LS(32, PHASE);   \
+    else JB_LAUNCH_LS(64, PHASE);                   \
+  } while (0)
+  if (!segmented) {
+    JB_LAUNCH_LS_R(WHOLE);
+    return 0;
+  }
+  JB_LAUNCH_LS_R(LOCAL);
+  {
+    const size_t per = (size_t)H * d * e;
+    jb::Launch cfg(dim3(n_seqs, (unsigned)((per + 255) / 256)), dim3(256), 0, stream);
+    cudaError_t err = cudaLaunchKernelEx(&cfg.c, lightning_prefix_kernel, scratch, (const float*)state, q_start, seq_slot,
+                                         decay, H, d, e, seg_len, tiles);
+    if (err != cudaSuccess) return (int)err;
+  }
+  JB_LAUNCH_LS_R(FROM_START);
+#undef JB_LAUNCH_LS_R
+#undef JB_LAUNCH_LS
+  return 0;
 }
 
 // out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * w * sigmoid(gate[t]); o: float32 [T, N]; gate: float32 rows of gate_ld.

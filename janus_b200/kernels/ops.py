@@ -64,9 +64,10 @@ _SIGNATURES = {
     "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
     "jb_streams_rmsnorm": "pppipifpiiipp", "jb_streams_mix": "ppppiiip", "jb_embed_streams": "pippiiippp",
-    "jb_lightning_scan": "piiiipppppiiiip", "jb_gated_rmsnorm": "ppipifpiiip",
+    "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
     "jb_conv_rope_cache": "pipippppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
+    "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
     "jb_clamped_glu": "piipiiiffp", "jb_scale_softcap": "plffp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
@@ -946,11 +947,16 @@ def streams_mix(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights
 
 
 # -- linear attention with decay ----------------------------------------------------------
+LIGHTNING_SEGMENT = 128       # tokens of a segment when a long prompt's recurrence runs in segments side by side
+
+
 def lightning_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, out: torch.Tensor, state: torch.Tensor,
                    q_start: torch.Tensor, seq_slot: torch.Tensor, decay: torch.Tensor, n_seqs: int, heads: int,
-                   dim: int, vdim: int) -> None:
+                   dim: int, vdim: int, max_q_len: int = 1, workspace=None) -> None:
     """Per sequence and head S <- decay S + silu(k_t) silu(v_t)^T, out_t = S^T silu(q_t) over the step's tokens in
-    order; proj float32 [T, ld] holds the raw q, k, v at the given columns; state float32 [slots, heads, dim, vdim]."""
+    order; proj float32 [T, ld] holds the raw q, k, v at the given columns; state float32 [slots, heads, dim, vdim].
+    With a workspace, steps whose longest sequence brings more than two segments of tokens run in three passes over
+    segments (their states from zero, a prefix pass, the outputs), 3 launches; else one launch."""
     T = proj.shape[0]
     _need(proj, "lightning projections", torch.float32)
     _need(out, "lightning out", torch.float32, (T, heads * vdim))
@@ -962,9 +968,15 @@ def lightning_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, out: 
     _need(decay, "decay", torch.float32, (heads,))
     if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim) > proj.shape[1]:
         raise KernelError("lightning_scan: the projections' columns reach past the rows")
+    seg, scratch = 0, None
+    if workspace is not None and max_q_len > 2 * LIGHTNING_SEGMENT:
+        seg = LIGHTNING_SEGMENT
+        tiles = (max_q_len + seg - 1) // seg
+        scratch = workspace.get("lightning_segments", (n_seqs * tiles * heads * dim * vdim,), torch.float32)
     _check(_lib("lightning").jb_lightning_scan(
         _ptr(proj), proj.shape[1], int(q_col), int(k_col), int(v_col), _ptr(out), _ptr(state), _ptr(q_start),
-        _ptr(seq_slot), _ptr(decay), n_seqs, heads, dim, vdim, _stream()), "lightning_scan")
+        _ptr(seq_slot), _ptr(decay), n_seqs, heads, dim, vdim, int(max_q_len), seg, _ptr(scratch), _stream()),
+        "lightning_scan", kernels=3 if seg else 1)
 
 
 def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -1043,6 +1055,40 @@ def diff_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
         _ptr(q), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(out), dtype_code(out.dtype),
         _ptr(block_table), _ptr(token_seq), _ptr(positions), T, heads, kv_heads, dim, vdim, page_size,
         block_table.shape[1], int(window), int(keep_first), scale, lam, eps, out_scale, _stream()), "diff_attention")
+
+
+DIFF_PREFILL_MAX_GROUP = 64     # query heads per key/value head that fit a tile of the tensor-core prompt kernel
+
+
+def diff_attention_prefill_supported(heads: int, kv_heads: int, dim: int, vdim: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel for prompt steps takes these sizes (bfloat16): key and value sizes that are
+    multiples of 16 up to 128, pages of 64 keys, at most 64 query heads per key/value head."""
+    return (_DIFF_MMA and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+            and page_size == 64 and kv_heads > 0 and heads % kv_heads == 0 and heads // kv_heads <= DIFF_PREFILL_MAX_GROUP)
+
+
+_DIFF_MMA = os.environ.get("JANUS_DIFF_MMA", "1") != "0"     # 0: prompts attend on the CUDA-core kernel
+
+
+def diff_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                           block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, n_seqs: int,
+                           max_q_len: int, heads: int, kv_heads: int, dim: int, vdim: int, page_size: int, window: int,
+                           keep_first: int, scale: float, lam: float, eps: float, out_scale: float) -> None:
+    """`diff_attention` for the new tokens of prompt steps (each sequence's last q_len positions of its kv_len) in
+    bfloat16 on the tensor cores; one library per (dim, vdim)."""
+    T = q.shape[0]
+    _need(q, "attention q", torch.float32, (T, heads * 2 * dim))
+    _need(out, "attention out", torch.bfloat16, (T, heads * vdim))
+    _need(k_cache, "k cache", torch.bfloat16)
+    _need(v_cache, "v cache", torch.bfloat16)
+    _need(block_table, "block table", torch.int32)
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(kv_len, "kv_len", torch.int32, (n_seqs,))
+    lib = _lib("diff_attention_mma", (int(dim), int(vdim)), lambda k: {"JB_DIFF_D": k[0], "JB_DIFF_E": k[1]})
+    _check(lib.jb_diff_attention_prefill(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len), n_seqs,
+        max_q_len, heads, kv_heads, dim, vdim, page_size, block_table.shape[1], int(window), int(keep_first), scale, lam,
+        eps, out_scale, _stream()), "diff_attention_prefill")
 
 
 # -- a gated activation with clamped branches; scale and soft cap -------------------------------

@@ -104,9 +104,16 @@ class DifferentialAttention(Mixer):
         if self.taps > 1:
             ops.conv_state_update(proj, cache_view.state, self.taps, ctx.q_start, ctx.seq_slot, ctx.n_seqs)
         attn = ws.get("diff_attn", (T, self.nh * self.vdim), self.dtype)
-        ops.diff_attention(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.token_seq, ctx.positions,
-                           self.nh, self.nkv, self.dim, self.vdim, group.page_size, self.window, self.keep_first,
-                           self.scale, self.lam, self.eps, 1.0 - self.diff)
+        if (self.dtype == torch.bfloat16 and not ctx.is_decode
+                and ops.diff_attention_prefill_supported(self.nh, self.nkv, self.dim, self.vdim, group.page_size)):
+            # prompt steps in bfloat16: the tensor-core kernel, a tile of tokens x the heads of a key/value head
+            ops.diff_attention_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start, ctx.kv_len,
+                                       ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, self.dim, self.vdim, group.page_size,
+                                       self.window, self.keep_first, self.scale, self.lam, self.eps, 1.0 - self.diff)
+        else:
+            ops.diff_attention(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.token_seq, ctx.positions,
+                               self.nh, self.nkv, self.dim, self.vdim, group.page_size, self.window, self.keep_first,
+                               self.scale, self.lam, self.eps, 1.0 - self.diff)
         self.o.forward_add(attn, residual)
 
 

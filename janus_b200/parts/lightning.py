@@ -63,7 +63,7 @@ class LightningAttention(Mixer):
         self.proj.forward(x, proj)
         o = ws.get("lightning_o", (T, self.v_width), torch.float32)
         ops.lightning_scan(proj, 0, self.qk_width, 2 * self.qk_width, o, cache_view.state, ctx.q_start, ctx.seq_slot,
-                           self.decay, ctx.n_seqs, self.nh, self.dim, self.vdim)
+                           self.decay, ctx.n_seqs, self.nh, self.dim, self.vdim, ctx.max_q_len, ws)
         gated = ws.get("lightning_gated", (T, self.v_width), self.dtype)
         ops.gated_rmsnorm(o, self.norm_weight, proj[:, 2 * self.qk_width + self.v_width:], self.eps, gated)
         self.o.forward_add(gated, residual)
