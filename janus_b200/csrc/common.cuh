@@ -89,6 +89,21 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(x);
 }
 
+// The activation of a gated product, act(gate) * up.  limit <= 0: SiLU, gate * sigmoid(gate) * up.  limit > 0: the
+// clamped form g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+struct Gate {
+  float limit;
+  float alpha;
+};
+__device__ __forceinline__ float gated(float g, float u, const Gate& gate) {
+  if (gate.limit > 0.0f) {
+    g = fminf(g, gate.limit);
+    u = fminf(fmaxf(u, -gate.limit), gate.limit) + 1.0f;
+    return g * (1.0f / (1.0f + expf(-gate.alpha * g))) * u;
+  }
+  return g * (1.0f / (1.0f + expf(-g))) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -13,7 +13,8 @@
 //                     `rot` dimensions of every q and k vector turn by the token's position (pairs
 //                     (i, i + rot/2), cos and sin from a table); q goes out in float32, k and v
 //                     into the cache.
-//   conv_state_update: the state takes the step's last projected values.
+//   conv_state_update: the state takes the step's last projected values (steps of one token per sequence do
+//                     this inside conv_rope_cache).
 //   diff_attention:   one block per (token, query head); both maps' online softmax over the visible
 //                     keys j <= i with (i - j < window or j < keep_first), in chunks of 32 keys that
 //                     start at multiples of 32 of the key index and go to the block's warps in turn (so
@@ -32,7 +33,7 @@ typedef __nv_bfloat16 bf16;
 
 template <typename TC>
 __global__ void conv_rope_cache_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w, int taps,
-                                       const float* __restrict__ conv_state, const int* __restrict__ token_seq,
+                                       float* __restrict__ conv_state, int update_state, const int* __restrict__ token_seq,
                                        const int* __restrict__ q_start, const int* __restrict__ seq_slot,
                                        const int* __restrict__ positions, const float* __restrict__ cos_sin, int rot,
                                        float* __restrict__ q_out, const int* __restrict__ dest, TC* __restrict__ k_cache,
@@ -43,7 +44,7 @@ __global__ void conv_rope_cache_kernel(const float* __restrict__ proj, int ld, c
   const int seq = token_seq[t];
   const int local = t - q_start[seq];                 // tokens of this sequence before t within the step
   const int Cq = H * 2 * d, Ck = G * 2 * d, Cv = G * e, C = Cq + Ck + Cv;
-  const float* st = conv_w ? conv_state + (size_t)seq_slot[seq] * (taps - 1) * C : nullptr;
+  float* st = (conv_w && taps > 1) ? conv_state + (size_t)seq_slot[seq] * (taps - 1) * C : nullptr;
   const int half = rot >> 1;
   const float* cs = cos_sin ? cos_sin + (size_t)positions[t] * half * 2 : nullptr;
   const int dst = dest[t];
@@ -72,20 +73,30 @@ __global__ void conv_rope_cache_kernel(const float* __restrict__ proj, int ld, c
       v_cache[(((size_t)page * G + g) * page_size + off) * e + i] = jb::from_f32<TC>(y);
     }
   };
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    if (c >= Cq + Ck || cs == nullptr) {
-      put(c, convolved(c));
-      continue;
-    }
-    const int i = (c < Cq ? c : c - Cq) % d;
-    if (i >= rot) {
-      put(c, convolved(c));
-    } else if (i < half) {
-      const float a = convolved(c), b = convolved(c + half);
-      const float co = cs[2 * i], si = cs[2 * i + 1];
-      put(c, a * co - b * si);
-      put(c + half, b * co + a * si);
-    }
+  // steps of one token per sequence: the thread that read a channel's state also moves it on by that token
+  auto shift = [&](int c) {
+    if (!update_state || st == nullptr) return;
+    for (int i = 0; i + 1 < taps - 1; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
+    st[(size_t)(taps - 2) * C + c] = proj[(size_t)t * ld + c];
+  };
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (c >= Cq + Ck || cs == nullptr) {
+    put(c, convolved(c));
+    shift(c);
+    return;
+  }
+  const int i = (c < Cq ? c : c - Cq) % d;
+  if (i >= rot) {
+    put(c, convolved(c));
+    shift(c);
+  } else if (i < half) {
+    const float a = convolved(c), b = convolved(c + half);
+    const float co = cs[2 * i], si = cs[2 * i + 1];
+    put(c, a * co - b * si);
+    put(c + half, b * co + a * si);
+    shift(c);
+    shift(c + half);
   }
 }
 
@@ -312,23 +323,25 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
 }  // namespace
 
 // proj: float32 [T, ld], columns [q: H 2 d | k: G 2 d | v: G e]; conv_w: float32 [C, taps] or null (no convolution);
-// conv_state: float32 [slots, taps - 1, C]; cos_sin: float32 [positions, rot / 2, 2] or null (no rotation);
+// conv_state: float32 [slots, taps - 1, C] (update_state: every sequence brings one token and the state takes it in
+// the same launch; otherwise `jb_conv_state_update` follows); cos_sin: float32 [positions, rot / 2, 2] or null (no rotation);
 // q_out: float32 [T, H 2 d]; dest[t] = page * page_size + row of token t in the caches (cache_dtype).
-JB_EXPORT int jb_conv_rope_cache(const float* proj, int ld, const float* conv_w, int taps, const float* conv_state,
-                                 const int* token_seq, const int* q_start, const int* seq_slot, const int* positions,
+JB_EXPORT int jb_conv_rope_cache(const float* proj, int ld, const float* conv_w, int taps, float* conv_state,
+                                 int update_state, const int* token_seq, const int* q_start, const int* seq_slot, const int* positions,
                                  const float* cos_sin, int rot, float* q_out, const int* dest, void* k_cache, void* v_cache,
                                  int cache_dtype, int T, int H, int G, int d, int e, int page_size, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(rot % 2 != 0 || rot > d || rot < 0, "conv_rope_cache: %d rotated dimensions do not fit vectors of %d", rot, d);
   JB_REFUSE(conv_w != nullptr && taps < 1, "conv_rope_cache: %d taps", taps);
   const int C = H * 2 * d + G * 2 * d + G * e;
-  jb::Launch cfg(dim3(T), dim3(C >= 1024 ? 256 : 128), 0, stream);
+  const int threads = C >= 1024 ? 256 : 128;
+  jb::Launch cfg(dim3(T, (C + threads - 1) / threads), dim3(threads), 0, stream);
   if (cache_dtype == JB_F32)
-    return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<float>, proj, ld, conv_w, taps, conv_state, token_seq,
+    return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<float>, proj, ld, conv_w, taps, conv_state, update_state, token_seq,
                                    q_start, seq_slot, positions, cos_sin, rot, q_out, dest, (float*)k_cache,
                                    (float*)v_cache, H, G, d, e, page_size);
   if (cache_dtype == JB_BF16)
-    return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<bf16>, proj, ld, conv_w, taps, conv_state, token_seq,
+    return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<bf16>, proj, ld, conv_w, taps, conv_state, update_state, token_seq,
                                    q_start, seq_slot, positions, cos_sin, rot, q_out, dest, (bf16*)k_cache, (bf16*)v_cache,
                                    H, G, d, e, page_size);
   return JB_ERR_BAD_DTYPE;

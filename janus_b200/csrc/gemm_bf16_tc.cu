@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(threads_for(BN)) gemm_tc_kernel(const __grid_c
                                                           int n_tiles, int n_tok_tiles, int n_w_tiles,
                                                           int up_tile_offset, int atomic_add,
                                                           float* __restrict__ partials, int* __restrict__ tickets,
-                                                          int* __restrict__ status) {
+                                                          jb::Gate gate, int* __restrict__ status) {
   using C = Cfg<BN, MODE>;
   constexpr int EPI_WARPS = epi_warps(BN), EPI_PARTS = EPI_WARPS / 4;
   extern __shared__ uint8_t smem_raw[];
@@ -464,8 +464,7 @@ __global__ void __launch_bounds__(threads_for(BN)) gemm_tc_kernel(const __grid_c
                   atomicAdd(((float*)Y) + o, v);
                 } else {
                   const float up = __uint_as_float(u[jj]);
-                  const float act = v * (1.0f / (1.0f + expf(-v)));
-                  ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(act * up);
+                  ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(jb::gated(v, up, gate));
                 }
               }
             }
@@ -551,7 +550,8 @@ struct Ordered {
 
 template <int BN, int MODE, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_out, int ldy, int k_tiles,
-           int split_k, int up_tile_offset, const Ordered& ordered, int* status, cudaStream_t stream) {
+           int split_k, int up_tile_offset, const Ordered& ordered, int* status, cudaStream_t stream,
+           jb::Gate gate = jb::Gate{0.0f, 1.0f}) {
   using C = Cfg<BN, MODE>;
   constexpr int smem = STAGES * C::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static int ctas_per_sm = 0;
@@ -588,19 +588,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_o
   return (int)cudaLaunchKernelEx(&cfg.c, gemm_tc_kernel<BN, MODE, STAGES>, mw, mx, Y, T, N_out, ldy, k_tiles, per,
                                  (int)n_tiles, n_tok_tiles, n_w_tiles, up_tile_offset, splits > 1 ? 1 : 0,
                                  in_order ? ordered.partials : (float*)nullptr, in_order ? ordered.tickets : (int*)nullptr,
-                                 status);
+                                 gate, status);
 }
 
 template <int MODE>
 int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, int K, int ldy, int split_k,
-             int up_tile_offset, const Ordered& ordered, int* status, cudaStream_t stream) {
+             int up_tile_offset, const Ordered& ordered, int* status, cudaStream_t stream,
+             jb::Gate gate = jb::Gate{0.0f, 1.0f}) {
   const int k_tiles = (K + BK - 1) / BK;
   CUtensorMap mx;
 #define JB_GO(BN_, ST_)                                                                                 \
   {                                                                                                     \
     if (!make_map(&mx, X, (uint64_t)T, (uint64_t)K, BN_)) return JB_ERR_TENSORMAP;                      \
     return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_tile_offset, ordered,   \
-                                  status, stream);                                                      \
+                                  status, stream, gate);                                                \
   }
   // Decode-sized token counts: small stages so that two or more CTAs share an SM
   // and keep enough loads in flight; prefill: wide tiles, deep ring.
@@ -621,7 +622,8 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
 // Y (+)= X . W^T.  X: [T, K] bf16 row-major; W: the [N_out, K] matrix packed by jb_pack_weight_bf16
 // (`w_tiles` tiles of 16 KB in all; for mode SWIGLU the gate rows' tiles first and the up rows' tiles from row
 // tile `up_tile_offset` on); Y: [T, ldy] with N_out columns used.
-// mode: 0 store bf16, 1 store f32, 2 add into f32, 3 silu(gate)*up -> bf16.
+// mode: 0 store bf16, 1 store f32, 2 add into f32, 3 act(gate)*up -> bf16 (`jb::gated` with gate_limit, gate_alpha:
+// limit <= 0 is SiLU).
 // split_k > 1 only with mode 2: partial sums meet in Y through atomic adds, or, if `partials` (room for
 // `partial_floats` floats) and `tickets` (`n_tickets` ints, zero) are given, in the fixed order of the slices:
 // tiles x slices x 128 x token tile floats and one ticket per output tile are needed (token tile: 16, 32, 64,
@@ -629,7 +631,8 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
 // `status` is a device int that a timed-out wait sets to 1 (producer), 2 (MMA) or 3 (epilogue).
 JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
                            int N_out, int K, int ldy, int mode, int split_k, float* partials, long long partial_floats,
-                           int* tickets, int n_tickets, int* status, cudaStream_t stream) {
+                           int* tickets, int n_tickets, float gate_limit, float gate_alpha, int* status,
+                           cudaStream_t stream) {
   const Ordered ordered{partials, partial_floats, tickets, n_tickets}, none{nullptr, 0, nullptr, 0};
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
@@ -649,6 +652,8 @@ JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, long long w_tiles, int 
       if (split_k > 1 && partials != nullptr)
         return dispatch<ADD_ORDERED>(mw, X, Y, T, N_out, K, ldy, split_k, 0, ordered, status, stream);
       return dispatch<ADD_F32>(mw, X, Y, T, N_out, K, ldy, split_k, 0, none, status, stream);
-    default: return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, up_tile_offset, none, status, stream);
+    default:
+      return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, up_tile_offset, none, status, stream,
+                              jb::Gate{gate_limit, gate_alpha});
   }
 }

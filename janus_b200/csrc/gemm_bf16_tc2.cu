@@ -226,7 +226,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
                                                            const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                            int T, int N_out, int ldy, int k_tiles, int n_tiles,
                                                            int n_tok_tiles, int k_per, int splits, int n_whole,
-                                                           int up_tile_offset, RopeOut rope, int* __restrict__ status) {
+                                                           int up_tile_offset, RopeOut rope, jb::Gate gate,
+                                                           int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -355,8 +356,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
 #pragma unroll
             for (int jj = 0; jj < 16; jj += 2) {
               const float g0 = __uint_as_float(r[jj]), g1 = __uint_as_float(r[jj + 1]);
-              const float a0 = g0 * (1.0f / (1.0f + expf(-g0))) * __uint_as_float(u[jj]);
-              const float a1 = g1 * (1.0f / (1.0f + expf(-g1))) * __uint_as_float(u[jj + 1]);
+              const float a0 = jb::gated(g0, __uint_as_float(u[jj]), gate);
+              const float a1 = jb::gated(g1, __uint_as_float(u[jj + 1]), gate);
               const __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
               packed[jj / 2] = *(const uint32_t*)&h;
             }
@@ -527,7 +528,8 @@ int sm_count() {
 
 template <int MODE>
 int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T, int N_out, int K, int ldy,
-           const RopeOut& rope, int* status, cudaStream_t stream, int split_k = 1, int whole_tiles = 0) {
+           const RopeOut& rope, int* status, cudaStream_t stream, int split_k = 1, int whole_tiles = 0,
+           jb::Gate gate = jb::Gate{0.0f, 1.0f}) {
   constexpr int smem = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -578,7 +580,8 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
     cfg.numAttrs = 2;
   }
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, Y, T, N_out, ldy, k_tiles, n_tiles,
-                                 n_tok_tiles, k_per, splits, n_whole, MODE == SWIGLU ? up_tile_offset : 0, rope, status);
+                                 n_tok_tiles, k_per, splits, n_whole, MODE == SWIGLU ? up_tile_offset : 0, rope, gate,
+                                 status);
 }
 
 }  // namespace
@@ -587,10 +590,11 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
 // cuts K of an adding product (mode ADD_F32) into that many slices, which meet in Y by atomic adds; the first
 // `whole_tiles` output tiles (256 x 256, token tile fastest) stay uncut: the tiles that fill whole waves of CTA
 // pairs, so that only the last, partial wave is cut.
+// Mode SWIGLU applies `jb::gated` with (gate_limit, gate_alpha): limit <= 0 is SiLU.
 // Meant for prompt-sized T.  status codes of a timed-out wait: 21 producer, 22 MMA, 23 epilogue.
 JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
-                                int N_out, int K, int ldy, int mode, int split_k, int whole_tiles, int* status,
-                                cudaStream_t stream) {
+                                int N_out, int K, int ldy, int mode, int split_k, int whole_tiles, float gate_limit,
+                                float gate_alpha, int* status, cudaStream_t stream) {
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16_pair: operands must be 16-byte aligned");
@@ -598,7 +602,9 @@ JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles,
     case STORE_BF16: return launch<STORE_BF16>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     case STORE_F32: return launch<STORE_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     case ADD_F32: return launch<ADD_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, split_k, whole_tiles);
-    case SWIGLU: return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case SWIGLU:
+      return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, 1, 0,
+                            jb::Gate{gate_limit, gate_alpha});
     default: JB_REFUSE(true, "gemm_bf16_pair: unknown mode %d", mode);
   }
 }

@@ -57,7 +57,7 @@ _SIGNATURES = {
     "jb_swiglu": "ppiiip", "jb_swiglu_f32_to_bf16": "piipiip", "jb_zero_f32": "plp",
     "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
     "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiifp",
-    "jb_gemm_bf16": "pplipiiiiiiplpipp", "jb_gemm_bf16_pair": "pplipiiiiiiipp",
+    "jb_gemm_bf16": "pplipiiiiiiplpiffpp", "jb_gemm_bf16_pair": "pplipiiiiiiiffpp",
     "jb_gemm_bf16_pair_qkv_rope": "ppliippppppiiiipp",
     "jb_sample": "piipfiffppupppp",
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
@@ -65,7 +65,7 @@ _SIGNATURES = {
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
     "jb_streams_rmsnorm": "pppipifpiiipp", "jb_streams_mix": "ppppiiip", "jb_embed_streams": "pippiiippp",
     "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
-    "jb_conv_rope_cache": "pipippppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
+    "jb_conv_rope_cache": "pipipipppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
     "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
     "jb_clamped_glu": "piipiiiffp", "jb_scale_softcap": "plffp",
@@ -583,11 +583,12 @@ _ATTN_TC = os.environ.get("JANUS_ATTN_TC", "1") != "0"     # 0: prompts attend o
 
 def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "store",
               split_k: Optional[int] = None, pair: Optional[bool] = None, whole_tiles: int = 0,
-              label: str = "") -> None:
+              label: str = "", gate_limit: float = 0.0, gate_alpha: float = 1.0) -> None:
     """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation; w packed (`pack_weight`).
     mode "store": y[T, N] = result (bf16 or float32 by y's dtype);
     mode "add":   y[T, N] += result, y float32 (K may be split, sums meet by atomic adds);
-    mode "swiglu": w a gated pair (`pack_gated`), y[T, N] = silu(gate) * up in bf16.
+    mode "swiglu": w a gated pair (`pack_gated`), y[T, N] = silu(gate) * up in bf16; with gate_limit > 0 the
+                   clamped form g sigmoid(gate_alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit).
     `split_k`, `pair`, `whole_tiles`: as `gemm_plan_whole` picks them unless given (`whole_tiles`: CTA pairs
     only, the first so many 256 x 256 output tiles of an adding product stay uncut)."""
     T, K = x.shape
@@ -625,7 +626,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     if pair:
         _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair(
             _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
-            int(split_k), int(whole_tiles), _ptr(kernel_status(x.device)), _stream()),
+            int(split_k), int(whole_tiles), gate_limit, gate_alpha, _ptr(kernel_status(x.device)), _stream()),
             "gemm_bf16_pair " + label if label else "gemm_bf16_pair")
         return
     partials = tickets = None
@@ -643,7 +644,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     _check(_lib("gemm_bf16_tc", _defines_key(_GEMM_DEFINES), _GEMM_DEFINES).jb_gemm_bf16(
         _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
         int(split_k), _ptr(partials), 0 if partials is None else partials.numel(), _ptr(tickets),
-        0 if tickets is None else tickets.numel(), _ptr(kernel_status(x.device)), _stream()),
+        0 if tickets is None else tickets.numel(), gate_limit, gate_alpha, _ptr(kernel_status(x.device)), _stream()),
         "gemm_bf16 " + label if label else "gemm_bf16")
 
 
@@ -998,9 +999,10 @@ def conv_rope_cache(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: in
                     token_seq: torch.Tensor, q_start: torch.Tensor, seq_slot: torch.Tensor, positions: torch.Tensor,
                     cos_sin: Optional[torch.Tensor], rot: int, q_out: torch.Tensor, dest: torch.Tensor,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
-                    page_size: int) -> None:
+                    page_size: int, update_state: bool = False) -> None:
     """Short causal convolution over time on every channel of the projected q, k, v (float32 [T, C]), rotation of
-    the first `rot` dimensions of every q and k vector, q out in float32, k and v into the paged caches."""
+    the first `rot` dimensions of every q and k vector, q out in float32, k and v into the paged caches.
+    `update_state`: every sequence brings one token and the convolution's state takes it in the same launch."""
     T = proj.shape[0]
     C = heads * 2 * dim + kv_heads * 2 * dim + kv_heads * vdim
     _need(proj, "projections", torch.float32, (T, C))
@@ -1023,7 +1025,7 @@ def conv_rope_cache(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: in
         if tuple(cos_sin.shape[1:]) != (rot // 2, 2):
             raise KernelError(f"conv_rope_cache: table of shape {tuple(cos_sin.shape)} does not fit {rot} rotated dimensions")
     _check(_lib("diff_attention").jb_conv_rope_cache(
-        _ptr(proj), proj.shape[1], _ptr(conv_w), int(taps), _ptr(conv_state), _ptr(token_seq), _ptr(q_start),
+        _ptr(proj), proj.shape[1], _ptr(conv_w), int(taps), _ptr(conv_state), int(update_state), _ptr(token_seq), _ptr(q_start),
         _ptr(seq_slot), _ptr(positions), _ptr(cos_sin), int(rot), _ptr(q_out), _ptr(dest), _ptr(k_cache), _ptr(v_cache),
         dtype_code(k_cache.dtype), T, heads, kv_heads, dim, vdim, page_size, _stream()), "conv_rope_cache")
 

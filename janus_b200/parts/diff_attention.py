@@ -100,8 +100,8 @@ class DifferentialAttention(Mixer):
         ops.conv_rope_cache(proj, self.conv_weight, self.taps, cache_view.state if self.taps > 1 else None,
                             ctx.token_seq, ctx.q_start, ctx.seq_slot, ctx.positions, table, self.rotary_dims, q,
                             group.dest_rows, cache_view.k, cache_view.v, self.nh, self.nkv, self.dim, self.vdim,
-                            group.page_size)
-        if self.taps > 1:
+                            group.page_size, update_state=ctx.is_decode)
+        if self.taps > 1 and not ctx.is_decode:
             ops.conv_state_update(proj, cache_view.state, self.taps, ctx.q_start, ctx.seq_slot, ctx.n_seqs)
         attn = ws.get("diff_attn", (T, self.nh * self.vdim), self.dtype)
         if (self.dtype == torch.bfloat16 and not ctx.is_decode

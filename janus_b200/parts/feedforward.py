@@ -5,7 +5,6 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
 from .base import FeedForward, register_part
 from .linear import GatedLinear, Linear
 
@@ -35,15 +34,17 @@ class SwiGLUFeedForward(FeedForward):
 
 class ClampedGLUFeedForward(FeedForward):
     """down( g * sigmoid(alpha g) * (u + 1) ) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit),
-    added into the residual stream.  Gate and up run as one product of the stacked rows into float32; the
-    activation reads the accumulators."""
+    added into the residual stream.  The gated product is the SwiGLU one with another activation in the same
+    epilogue (`GatedLinear` with a limit)."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
                  dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
+        if not limit > 0.0:
+            raise ValueError(f"the clamp's limit must be positive, got {limit}")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.limit, self.alpha = float(limit), float(alpha)
         self.dtype, self.device = dtype, device
-        self.gate_up = Linear(hidden_size, 2 * intermediate_size, dtype, device, name="gate_up")
+        self.gate_up = GatedLinear(hidden_size, intermediate_size, dtype, device, limit=self.limit, alpha=self.alpha)
         self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down")
 
     def weight_shapes(self):
@@ -52,15 +53,12 @@ class ClampedGLUFeedForward(FeedForward):
                 "down": ((self.hidden_size, self.intermediate_size), "normal")}
 
     def load(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> None:
-        self.gate_up.load([gate, up])
+        self.gate_up.load(gate, up)
         self.down.load([down])
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
-        T, I = x.shape[0], self.intermediate_size
-        gu = ctx.workspace.get("gate_up", (T, 2 * I), torch.float32)
-        self.gate_up.forward(x, gu)
-        act = ctx.workspace.get("ffn_act", (T, I), self.dtype)
-        ops.clamped_glu(gu, act, I, self.limit, self.alpha)
+        act = ctx.workspace.get("ffn_act", (x.shape[0], self.intermediate_size), self.dtype)
+        self.gate_up.forward(x, act, ctx)
         self.down.forward_add(act, residual)
 
 

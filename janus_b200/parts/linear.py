@@ -93,11 +93,14 @@ class Linear:
 
 class GatedLinear:
     """out = silu(x Wg^T) * (x Wu^T) with Wg stacked over Wu
-    (crates/janus-engine/src/model/block.rs:383-430)."""
+    (crates/janus-engine/src/model/block.rs:383-430).  With `limit` > 0 the activation is the clamped form
+    g * sigmoid(alpha g) * (u + 1), g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), in the same places:
+    the product's own epilogue, or the activation kernel behind a plain product."""
 
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device,
-                 name: str = "gate_up"):
+                 name: str = "gate_up", limit: float = 0.0, alpha: float = 1.0):
         _check_width(in_features, dtype)
+        self.limit, self.alpha = float(limit), float(alpha)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
         self.name = name
@@ -117,13 +120,20 @@ class GatedLinear:
         if self.dtype == torch.float32:
             gu = ctx.workspace.get("gate_up", (x.shape[0], 2 * self.out_features), torch.float32)
             ops.gemm_f32(x, self.weight, gu, accumulate=False, label=self.name)
-            ops.swiglu(gu, out)
+            if self.limit > 0.0:
+                ops.clamped_glu(gu, out, self.out_features, self.limit, self.alpha)
+            else:
+                ops.swiglu(gu, out)
         elif ops.gated_runs_unfused(x.shape[0], self.out_features):
             # few tokens, narrow layer: twice the tiles stream the weights as a plain product; the gate is applied after
             if self._stacked is None:
                 self._stacked = self.weight.stacked()
             gu = ctx.workspace.get("gate_up", (x.shape[0], self._stacked.rows), torch.float32)
             ops.gemm_bf16(x, self._stacked, gu, mode="store", pair=False, label=self.name)
-            ops.swiglu_f32_to_bf16(gu, out, 128 * self.weight.up_tile_offset)
+            if self.limit > 0.0:
+                ops.clamped_glu(gu, out, 128 * self.weight.up_tile_offset, self.limit, self.alpha)
+            else:
+                ops.swiglu_f32_to_bf16(gu, out, 128 * self.weight.up_tile_offset)
         else:
-            ops.gemm_bf16(x, self.weight, out, mode="swiglu", label=self.name)
+            ops.gemm_bf16(x, self.weight, out, mode="swiglu", label=self.name, gate_limit=self.limit,
+                          gate_alpha=self.alpha)
