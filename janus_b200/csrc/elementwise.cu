@@ -394,3 +394,25 @@ JB_EXPORT int jb_scale_softcap(float* x, long long n, float scale, float cap, cu
   jb::Launch cfg(dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, scale_softcap_kernel, x, scale, cap, (size_t)n);
 }
+
+// Rows of K bfloat16 copied into rows of Kp >= K with zeros behind them: the operand of a tensor-core product whose
+// width is no multiple of 8 (its weight is padded the same way when it is loaded).
+namespace {
+__global__ void pad_rows_bf16_kernel(const bf16* __restrict__ x, int K, bf16* __restrict__ out, int Kp, size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / Kp;
+  const int c = (int)(i % Kp);
+  out[i] = c < K ? x[t * K + c] : __float2bfloat16_rn(0.0f);
+}
+}  // namespace
+
+JB_EXPORT int jb_pad_rows_bf16(const void* x, int K, void* out, int Kp, int T, cudaStream_t stream) {
+  const size_t n = (size_t)T * Kp;
+  if (n == 0) return 0;
+  JB_REFUSE(Kp < K, "pad_rows: rows of %d do not hold %d", Kp, K);
+  jb::Launch cfg(dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, pad_rows_bf16_kernel, (const bf16*)x, K, (bf16*)out, Kp, n);
+}

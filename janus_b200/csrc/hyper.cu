@@ -8,6 +8,7 @@
 //                    one block per row; it can clear the row r of a float32 [rows, H] buffer
 //                    besides (the target the sublayer adds its output into).
 //   streams_mix:     the rewrite, in place, one thread per (token, column).
+//   streams_mix_rmsnorm: a sublayer's rewrite and the next sublayer's read in one launch.
 //
 // All sums run over s = 0, 1, ... in that order in float32, so a token's values do not depend
 // on what else is in the step.
@@ -41,6 +42,57 @@ __global__ void streams_rmsnorm_kernel(const float* __restrict__ x, const int* _
     u_s[i] = u;
     ss += u * u;
     if (clear) clear[(size_t)r * H + i] = 0.0f;
+  }
+  ss = jb::block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    o[i] = jb::from_f32<TO>((u_s[i] / rms) * jb::to_f32(gamma[i]));
+}
+
+// The rewrite of the streams by the sublayer that has just run (y, M, b) and the read of the next sublayer
+// (a, gamma) in one launch: a block owns a token, rewrites its streams in place, sums them with the next
+// sublayer's weights as it goes, clears the row of y, and norms.  The same sums in the same order as
+// streams_mix followed by streams_rmsnorm.
+template <typename TG, typename TO>
+__global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ M,
+                                           const float* __restrict__ b, const float* __restrict__ a, int S,
+                                           const TG* __restrict__ gamma, float eps, TO* __restrict__ out, int H) {
+  extern __shared__ float u_s[];          // H floats, then 33 of scratch, then M, b, a
+  float* scratch = u_s + H;
+  float* m_s = scratch + 33;
+  if (threadIdx.x < S * S) m_s[threadIdx.x] = M[threadIdx.x];
+  if (threadIdx.x < S) {
+    m_s[MAX_STREAMS * MAX_STREAMS + threadIdx.x] = b[threadIdx.x];
+    m_s[MAX_STREAMS * MAX_STREAMS + MAX_STREAMS + threadIdx.x] = a[threadIdx.x];
+  }
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  __syncthreads();
+  const int r = blockIdx.x;
+  float* xr = x + (size_t)r * S * H;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float old[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < S ? xr[(size_t)s * H + i] : 0.0f;
+    const float yv = y[(size_t)r * H + i];
+    float u = 0.0f;
+#pragma unroll
+    for (int to = 0; to < MAX_STREAMS; ++to) {
+      if (to < S) {
+        float v = 0.0f;
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s)
+          if (s < S) v = fmaf(m_s[s * S + to], old[s], v);
+        v = fmaf(m_s[MAX_STREAMS * MAX_STREAMS + to], yv, v);
+        xr[(size_t)to * H + i] = v;
+        u = fmaf(m_s[MAX_STREAMS * MAX_STREAMS + MAX_STREAMS + to], v, u);
+      }
+    }
+    u_s[i] = u;
+    ss += u * u;
+    y[(size_t)r * H + i] = 0.0f;
   }
   ss = jb::block_sum(ss, scratch);
   const float rms = sqrtf(ss / (float)H + eps);
@@ -116,6 +168,33 @@ JB_EXPORT int jb_streams_mix(float* x, const float* y, const float* M, const flo
   const size_t n = (size_t)T * H;
   jb::Launch cfg(dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, streams_mix_kernel, x, y, M, b, S, H, n);
+}
+
+// x: float32 [T, S, H] rewritten in place by (y, M, b) as in jb_streams_mix; then out[t] = rmsnorm(sum_s a[s] x[t, s]) *
+// gamma and y[t] = 0, as jb_streams_rmsnorm with `clear` would do next.
+JB_EXPORT int jb_streams_mix_rmsnorm(float* x, float* y, const float* M, const float* b, const float* a, int S,
+                                     const void* gamma, int gamma_dtype, float eps, void* out, int out_dtype, int T, int H,
+                                     cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(S < 1 || S > MAX_STREAMS, "streams_mix_rmsnorm: %d streams are outside [1, %d]", S, MAX_STREAMS);
+  const size_t smem = (size_t)(H + 33 + MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS) * sizeof(float);
+  JB_REFUSE(smem > 200 * 1024, "streams_mix_rmsnorm: rows of %d floats do not fit shared memory", H);
+  jb::Launch cfg(dim3(T), dim3(H >= 2048 ? 256 : 128), smem, stream);
+  cudaError_t e = cudaSuccess;
+#define JB_LAUNCH_SMN(TG, TO)                                                                                       \
+  do {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(streams_mix_rmsnorm_kernel<TG, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    e = cudaLaunchKernelEx(&cfg.c, streams_mix_rmsnorm_kernel<TG, TO>, x, y, M, b, a, S, (const TG*)gamma, eps,     \
+                           (TO*)out, H);                                                                            \
+  } while (0)
+  if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_SMN(float, float);
+  else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_SMN(float, bf16);
+  else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_SMN(bf16, float);
+  else if (gamma_dtype == JB_BF16 && out_dtype == JB_BF16) JB_LAUNCH_SMN(bf16, bf16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_SMN
+  return (int)e;
 }
 
 namespace {

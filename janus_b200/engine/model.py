@@ -39,7 +39,7 @@ class DecoderModel:
         self.embedding_transforms = [make_part("transform", ps, dtype, device) for ps in spec.embedding_transforms]
         self.logit_transforms = [make_part("transform", ps, dtype, device) for ps in spec.logit_transforms]
         self.embedding: Optional[torch.Tensor] = None
-        self.head = Linear(spec.hidden_size, spec.vocab_size, dtype, device, name="head")
+        self.head = Linear(spec.hidden_size, spec.vocab_size, dtype, device, name="head", pad_width=spec.pad_head_width)
         self.schedule = list(spec.schedule)
         for place, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
@@ -107,10 +107,15 @@ class DecoderModel:
                               ctx.seq_slot if ctx.feedback is not None else None)
         for transform in self.embedding_transforms:
             transform.forward(residual, ctx)
+        ctx.pending_write = None
         for place, entry in enumerate(self.schedule):
             view = ctx.cache_view(place if entry.reads_cache_of is None else entry.reads_cache_of)
             with log.nvtx_range(f"place {place}: layer {entry.layer}"):
                 self.layers[entry.layer].forward(residual, ctx, view, writes_cache=entry.reads_cache_of is None)
+        if ctx.pending_write is not None:       # the last sublayer's write into the residual streams
+            connection, y = ctx.pending_write
+            connection.write(residual, y)
+            ctx.pending_write = None
         n_want = want_rows.shape[0]
         if n_want == 0:
             return

@@ -72,6 +72,9 @@ class StepContext:
         self.workspace: Workspace = None
         self.cache: SequenceCache = None
         self.dtype: torch.dtype = None
+        # (connection, y) of a sublayer whose write into the residual streams is still to come: an arrangement
+        # may leave it for the next read to do in the same launch; the model flushes it after the last layer
+        self.pending_write = None
 
     def cache_view(self, place: int) -> CacheView:
         cache = self.cache

@@ -63,12 +63,12 @@ _SIGNATURES = {
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
     "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
-    "jb_streams_rmsnorm": "pppipifpiiipp", "jb_streams_mix": "ppppiiip", "jb_embed_streams": "pippiiippp",
+    "jb_streams_rmsnorm": "pppipifpiiipp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiip", "jb_embed_streams": "pippiiippp",
     "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
     "jb_conv_rope_cache": "pipipipppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
     "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
-    "jb_clamped_glu": "piipiiiffp", "jb_scale_softcap": "plffp",
+    "jb_clamped_glu": "piipiiiffp", "jb_pad_rows_bf16": "pipiip", "jb_scale_softcap": "plffp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
            "f": ctypes.c_float}
@@ -947,6 +947,24 @@ def streams_mix(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights
            "streams_mix")
 
 
+def streams_mix_rmsnorm(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights: torch.Tensor,
+                        next_weights: torch.Tensor, streams: int, gamma: torch.Tensor, eps: float,
+                        out: torch.Tensor) -> None:
+    """`streams_mix(x, y, mix, out_weights)` and then `streams_rmsnorm(x, next_weights, gamma) -> out` with y
+    cleared, in one launch and with the same sums."""
+    T, H = y.shape
+    _need(x, "streams x", torch.float32, (T, streams * H))
+    _need(y, "sublayer output", torch.float32)
+    _need(mix, "stream mix", torch.float32, (streams, streams))
+    _need(out_weights, "stream out weights", torch.float32, (streams,))
+    _need(next_weights, "stream weights", torch.float32, (streams,))
+    _need(gamma, "streams gamma", None, (H,))
+    _need(out, "streams out", None, (T, H))
+    _check(_lib("hyper").jb_streams_mix_rmsnorm(
+        _ptr(x), _ptr(y), _ptr(mix), _ptr(out_weights), _ptr(next_weights), int(streams), _ptr(gamma),
+        dtype_code(gamma.dtype), eps, _ptr(out), dtype_code(out.dtype), T, H, _stream()), "streams_mix_rmsnorm")
+
+
 # -- linear attention with decay ----------------------------------------------------------
 LIGHTNING_SEGMENT = 128       # tokens of a segment when a long prompt's recurrence runs in segments side by side
 
@@ -1109,3 +1127,13 @@ def scale_softcap(x: torch.Tensor, scale: float, cap: float) -> None:
     """x <- cap * tanh(x * scale / cap) in place (cap <= 0: x * scale); float32."""
     _need(x, "logits", torch.float32)
     _check(_lib("elementwise").jb_scale_softcap(_ptr(x), x.numel(), scale, cap, _stream()), "scale_softcap")
+
+
+def pad_rows_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :K] = x[t], out[t, K:] = 0 for bfloat16 rows: the operand of a product whose width was padded."""
+    T, K = x.shape
+    _need(x, "rows to pad", torch.bfloat16)
+    _need(out, "padded rows", torch.bfloat16)
+    if out.shape[0] != T or out.shape[1] < K:
+        raise KernelError(f"pad_rows: {tuple(out.shape)} does not hold {tuple(x.shape)}")
+    _check(_lib("elementwise").jb_pad_rows_bf16(_ptr(x), K, _ptr(out), out.shape[1], T, _stream()), "pad_rows")

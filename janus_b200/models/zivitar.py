@@ -73,7 +73,7 @@ def zivitar_spec(config: ZivitarConfig) -> ModelSpec:
         schedule=tuple(ScheduleEntry(index_of[config.owner(i)]) for i in range(len(config.layers))),
         final_norm=PartSpec("rms_norm", dict(width=config.width, eps=config.eps), weights=dict(gamma="final.norm")),
         embedding_weight="embed", head_weight="head", max_positions=config.max_positions,
-        logit_transforms=transforms, residual_streams=config.streams or 1)
+        logit_transforms=transforms, residual_streams=config.streams or 1, pad_head_width=True)
 
 
 def build_zivitar(config: ZivitarConfig, dtype, device):

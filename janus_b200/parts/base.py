@@ -153,6 +153,8 @@ class ModelSpec:
     # copies of the residual stream per token (hyper-connections): the residual tensor of a step is
     # [T, residual_streams * hidden_size], every copy starts as the embedding, and the final norm reads their sum
     residual_streams: int = 1
+    # the head's product over a width that is no multiple of 8 runs on zero-padded operands in bfloat16 (False: refused)
+    pad_head_width: bool = False
 
 
 # --------------------------------------------------------------------------

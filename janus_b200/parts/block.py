@@ -72,14 +72,27 @@ class HyperConnectedBlock:
         T = residual.shape[0]
         x = ctx.workspace.get("normed", (T, self.hidden_size), self.dtype)
         y = ctx.workspace.get("sublayer_out", (T, self.hidden_size), torch.float32)
-        self.mixer_connection.read(residual, self.mixer_norm, x, clear=y)
+        # a sublayer's write waits for the read that follows it (the next sublayer's, also the next layer's) and
+        # runs in the same launch; the model flushes the last one before its final norm
+        pending = ctx.pending_write
+        ctx.pending_write = None
+        if pending is not None and pending[1] is y and hasattr(pending[0], "write_then_read"):
+            pending[0].write_then_read(residual, y, self.mixer_connection, self.mixer_norm, x)
+        else:
+            if pending is not None:
+                pending[0].write(residual, pending[1])
+            self.mixer_connection.read(residual, self.mixer_norm, x, clear=y)
         self.mixer.forward(x, y, ctx, cache_view, writes_cache)
-        self.mixer_connection.write(residual, y)
-        if self.feed_forward is None:
-            return
-        self.feed_forward_connection.read(residual, self.feed_forward_norm, x, clear=y)
-        self.feed_forward.forward(x, y, ctx)
-        self.feed_forward_connection.write(residual, y)
+        last = self.mixer_connection
+        if self.feed_forward is not None:
+            if hasattr(last, "write_then_read"):
+                last.write_then_read(residual, y, self.feed_forward_connection, self.feed_forward_norm, x)
+            else:
+                last.write(residual, y)
+                self.feed_forward_connection.read(residual, self.feed_forward_norm, x, clear=y)
+            self.feed_forward.forward(x, y, ctx)
+            last = self.feed_forward_connection
+        ctx.pending_write = (last, y)
 
 
 register_part("arrangement", "hyper_pre_norm", HyperConnectedBlock)

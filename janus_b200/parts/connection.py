@@ -46,5 +46,16 @@ class HyperConnection(Connection):
     def write(self, residual: torch.Tensor, y: torch.Tensor) -> None:
         ops.streams_mix(residual, y, self.mix, self.b, self.streams)
 
+    def write_then_read(self, residual: torch.Tensor, y: torch.Tensor, then: "HyperConnection", norm,
+                        out: torch.Tensor) -> None:
+        """This sublayer's write and the next sublayer's read (`then`, with its norm) in one launch; y is
+        left zeroed for the next sublayer to add into."""
+        gamma, eps = getattr(norm, "gamma", None), getattr(norm, "eps", None)
+        if isinstance(then, HyperConnection) and then.streams == self.streams and gamma is not None and eps is not None:
+            ops.streams_mix_rmsnorm(residual, y, self.mix, self.b, then.a, self.streams, gamma, eps, out)
+        else:
+            self.write(residual, y)
+            then.read(residual, norm, out, clear=y)
+
 
 register_part("connection", "hyper_connection", HyperConnection)

@@ -48,8 +48,8 @@ class DifferentialAttention(Mixer):
         self.rotary_dims = int(rotary_dims) if position is not None else 0
         self.q_width, self.k_width, self.v_width = self.nh * 2 * self.dim, self.nkv * 2 * self.dim, self.nkv * self.vdim
         self.channels = self.q_width + self.k_width + self.v_width
-        self.qkv = Linear(hidden_size, self.channels, dtype, device, name="qkv")
-        self.o = Linear(self.nh * self.vdim, hidden_size, dtype, device, name="o")
+        self.qkv = Linear(hidden_size, self.channels, dtype, device, name="qkv", pad_width=True)
+        self.o = Linear(self.nh * self.vdim, hidden_size, dtype, device, name="o", pad_width=True)
         self.conv_weight: Optional[torch.Tensor] = None
         self.lam = self.diff
 

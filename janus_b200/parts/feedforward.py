@@ -44,8 +44,10 @@ class ClampedGLUFeedForward(FeedForward):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.limit, self.alpha = float(limit), float(alpha)
         self.dtype, self.device = dtype, device
-        self.gate_up = GatedLinear(hidden_size, intermediate_size, dtype, device, limit=self.limit, alpha=self.alpha)
-        self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down")
+        # widths that are no multiple of 8 run on zero-padded operands
+        self.gate_up = GatedLinear(hidden_size, intermediate_size, dtype, device, limit=self.limit, alpha=self.alpha,
+                                   pad_width=True)
+        self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down", pad_width=True)
 
     def weight_shapes(self):
         return {"gate": ((self.intermediate_size, self.hidden_size), "normal"),

@@ -33,8 +33,8 @@ class LightningAttention(Mixer):
         self.qk_width, self.v_width = self.nh * self.dim, self.nh * self.vdim
         self.decay = torch.tensor([float(x) for x in decay], dtype=torch.float32, device=device)
         # rows of the stacked product: q, k, v, g
-        self.proj = Linear(hidden_size, 2 * self.qk_width + 2 * self.v_width, dtype, device, name="qkvg")
-        self.o = Linear(self.v_width, hidden_size, dtype, device, name="o")
+        self.proj = Linear(hidden_size, 2 * self.qk_width + 2 * self.v_width, dtype, device, name="qkvg", pad_width=True)
+        self.o = Linear(self.v_width, hidden_size, dtype, device, name="o", pad_width=True)
         self.norm_weight: Optional[torch.Tensor] = None
 
     def cache_spec(self) -> StateSpec:

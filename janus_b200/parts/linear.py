@@ -27,13 +27,46 @@ def _check_width(in_features: int, dtype: torch.dtype) -> None:
                          f"must be a multiple of 8); such a model runs with dtype float32")
 
 
+class _PaddedOperand:
+    """For a `Linear(pad_width=True)` whose width is no multiple of 8: the weight gets zero columns up to the next
+    multiple when it is loaded, and every call copies its rows into a buffer of that width with zeros behind them
+    (one small launch).  Buffers only grow and outgrown ones are kept, since a captured decode step holds their
+    address."""
+
+    def __init__(self, in_features: int, device: torch.device):
+        self.width = (in_features + 7) // 8 * 8
+        self.device = device
+        self._buffers = []
+
+    def weight(self, w: torch.Tensor) -> torch.Tensor:
+        pad = torch.zeros((w.shape[0], self.width - w.shape[1]), dtype=w.dtype, device=w.device)
+        return torch.cat([w, pad], dim=1).contiguous()
+
+    def rows(self, x: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        if not self._buffers or self._buffers[-1].shape[0] < T:
+            rows = 64
+            while rows < T:
+                rows *= 2
+            self._buffers.append(torch.empty((rows, self.width), dtype=torch.bfloat16, device=self.device))
+        out = self._buffers[-1][:T]
+        ops.pad_rows_bf16(x, out)
+        return out
+
+
 class Linear:
     """One weight matrix, possibly the row-wise stack of several tensors of the
     checkpoint (q, k, v stacked so that one product serves all three)."""
 
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device,
-                 name: str = ""):
-        _check_width(in_features, dtype)
+                 name: str = "", pad_width: bool = False):
+        """`pad_width`: a bfloat16 product over a width that is no multiple of 8 runs on zero-padded copies of its
+        operands instead of being refused."""
+        self._padded = None
+        if pad_width and dtype == torch.bfloat16 and in_features % 8 != 0:
+            self._padded = _PaddedOperand(in_features, device)
+        else:
+            _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
         self.name = name     # what a profile of a step calls this product
@@ -45,6 +78,8 @@ class Linear:
         if tuple(w.shape) != (self.out_features, self.in_features):
             raise ValueError(f"weight of shape {tuple(w.shape)} does not fit "
                              f"({self.out_features}, {self.in_features})")
+        if self._padded is not None:
+            w = self._padded.weight(w)
         # bfloat16 products stream their weights as packed tiles (ops.PackedWeight); float32 stays row-major
         self.weight = ops.pack_weight(w) if self.dtype == torch.bfloat16 else w
 
@@ -65,10 +100,15 @@ class Linear:
         """Whether `forward` into a float32 `y` for this many tokens cuts K into slices that
         meet in `y` by atomic adds, so that `y` has to be zero beforehand."""
         return (self.dtype != torch.float32 and y_dtype == torch.float32
-                and ops.split_k_for(tokens, self.out_features, self.in_features) > 1)
+                and ops.split_k_for(tokens, self.out_features, self._k()) > 1)
+
+    def _k(self) -> int:
+        return self.in_features if self._padded is None else self._padded.width
 
     # y = x W^T, stored in y's dtype (engine dtype, or float32 for logits)
     def forward(self, x: torch.Tensor, y: torch.Tensor, y_is_zero: bool = False) -> None:
+        if self._padded is not None:
+            x = self._padded.rows(x)
         if self.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, y, accumulate=False, label=self.name)
         elif self.meets_by_adds(x.shape[0], y.dtype):
@@ -85,6 +125,8 @@ class Linear:
 
     # residual += x W^T, the sum made in float32
     def forward_add(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        if self._padded is not None:
+            x = self._padded.rows(x)
         if self.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, residual, accumulate=True, label=self.name)
         else:
@@ -98,8 +140,12 @@ class GatedLinear:
     the product's own epilogue, or the activation kernel behind a plain product."""
 
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device,
-                 name: str = "gate_up", limit: float = 0.0, alpha: float = 1.0):
-        _check_width(in_features, dtype)
+                 name: str = "gate_up", limit: float = 0.0, alpha: float = 1.0, pad_width: bool = False):
+        self._padded = None
+        if pad_width and dtype == torch.bfloat16 and in_features % 8 != 0:
+            self._padded = _PaddedOperand(in_features, device)      # as `Linear(pad_width=True)`
+        else:
+            _check_width(in_features, dtype)
         self.limit, self.alpha = float(limit), float(alpha)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
@@ -113,10 +159,14 @@ class GatedLinear:
             if tuple(t.shape) != (self.out_features, self.in_features):
                 raise ValueError(f"gate/up weight of shape {tuple(t.shape)} does not fit "
                                  f"({self.out_features}, {self.in_features})")
+        if self._padded is not None:
+            g, u = self._padded.weight(g), self._padded.weight(u)
         self.weight = ops.pack_gated(g, u) if self.dtype == torch.bfloat16 else torch.cat([g, u], dim=0)
         self._stacked = None
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, ctx) -> None:
+        if self._padded is not None:
+            x = self._padded.rows(x)
         if self.dtype == torch.float32:
             gu = ctx.workspace.get("gate_up", (x.shape[0], 2 * self.out_features), torch.float32)
             ops.gemm_f32(x, self.weight, gu, accumulate=False, label=self.name)

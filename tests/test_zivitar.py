@@ -68,7 +68,11 @@ CFG_D = dict(architecture="Zivitar", vocab=128, width=64, norm=dict(eps=1e-5), s
              layers=[layer("attention", attention(6, 2, 32, 48, 0.2, 0.5, conv=3, mask=(37, 2), rot=(16, 300.0)), 64, 1.0),
                      layer("attention", attention(2, 2, 16, 64, 0.3, 0.2, rot=(16, 10000.0, (4.0, 32, 16.0, 1.0)))),
                      layer("lightning", dict(heads=2, dim=32, vdim=32, decay=[0.99, 0.9]), 32, 1.0)])
-CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}
+# widths that are multiples of nothing: the bfloat16 products run on zero-padded operands, loads are scalar
+CFG_E = dict(architecture="Zivitar", vocab=75, width=36, norm=dict(eps=1e-5), streams=2,
+             layers=[layer("attention", attention(2, 1, 10, 7, 0.3, 0.3, conv=3, mask=(33, 1), rot=(6, 100.0)), 22, 1.0),
+                     layer("lightning", dict(heads=3, dim=5, vdim=9, decay=[0.9, 0.95, 0.99]), 13, 2.0)])
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
 
 
 def sharpened(w, factor=4.0):
@@ -220,7 +224,7 @@ def test_stream_kernels_activation_and_cap_against_their_formulas():
 
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompts_of_unequal_lengths_in_one_step(tmp_path, name, dtype):
     from janus_b200.engine import StepEntry
     cfg = CONFIGS[name]
