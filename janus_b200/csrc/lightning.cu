@@ -6,7 +6,7 @@
 //   with q = silu(.), k = silu(.), v = silu(.) of the projection's float32 output.
 //
 // lightning_scan: a block owns one (sequence, head, block of EB value columns); a thread owns
-// one value column and a quarter of the rows of S in registers, walks the tokens in order
+// two value columns and a quarter of the rows of S in registers, walks the tokens in order
 // (chunks of CT tokens are staged in shared memory, activated on the way), and the four
 // partial sums of o meet by shuffles in a fixed order.  The state is read from and written back
 // to the sequence's slot, so prompts, portions of prompts and single tokens are the same code.
@@ -29,7 +29,7 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 constexpr int PARTS = 4;      // threads that share a value column (each a quarter of the rows)
-constexpr int EB = 32;        // value columns a block owns
+constexpr int EB = 64;        // value columns a block owns, two a thread
 constexpr int CT = 16;        // tokens staged at a time
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -38,7 +38,7 @@ enum { WHOLE = 0, LOCAL = 1, FROM_START = 3 };
 
 // RMAX: rows of S a thread holds (a multiple of 4, 4 RMAX >= d); shared rows are padded to 4 RMAX with zeros
 template <int RMAX>
-__global__ void __launch_bounds__(EB * PARTS) lightning_scan_kernel(
+__global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
     const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, float* __restrict__ out,
     float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ seq_slot,
     const float* __restrict__ decay, int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch,
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(EB * PARTS) lightning_scan_kernel(
   const int seq = blockIdx.x / tiles_per_seq, seg = blockIdx.x % tiles_per_seq;
   const int h = blockIdx.y, e0 = blockIdx.z * EB;
   const int part = threadIdx.x % PARTS, col = threadIdx.x / PARTS;
-  const int j = e0 + col;
+  const int j0 = e0 + 2 * col, j1 = j0 + 1;
   const float lam = decay[h];
   jb::pdl_wait();
   const int s0 = q_start[seq], q_len = q_start[seq + 1] - s0;
@@ -63,11 +63,12 @@ __global__ void __launch_bounds__(EB * PARTS) lightning_scan_kernel(
   float* st = state + (((size_t)seq_slot[seq] * H + h) * d) * e;     // [d][e]
   float* sc = scratch ? scratch + (((size_t)blockIdx.x * H + h) * d) * e : nullptr;
   const float* init = phase == WHOLE ? st : phase == FROM_START ? sc : nullptr;
-  float S[RMAX];
+  float S0[RMAX], S1[RMAX];
 #pragma unroll
   for (int i = 0; i < RMAX; ++i) {
     const int r = part * RMAX + i;
-    S[i] = (init && r < d && j < e) ? init[(size_t)r * e + j] : 0.0f;
+    S0[i] = (init && r < d && j0 < e) ? init[(size_t)r * e + j0] : 0.0f;
+    S1[i] = (init && r < d && j1 < e) ? init[(size_t)r * e + j1] : 0.0f;
   }
   for (int c0 = t0; c0 < t1; c0 += CT) {
     const int n = min(CT, t1 - c0);
@@ -84,28 +85,42 @@ __global__ void __launch_bounds__(EB * PARTS) lightning_scan_kernel(
     }
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
-      const float v = v_s[tt * EB + col];
+      const float2 v = *reinterpret_cast<const float2*>(v_s + tt * EB + 2 * col);
       const float4* qr = reinterpret_cast<const float4*>(q_s + tt * DP + part * RMAX);
       const float4* kr = reinterpret_cast<const float4*>(k_s + tt * DP + part * RMAX);
-      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
 #pragma unroll
       for (int i = 0; i < RMAX / 4; ++i) {
         const float4 k4 = kr[i], q4 = qr[i];
-        S[4 * i] = fmaf(lam, S[4 * i], k4.x * v);
-        S[4 * i + 1] = fmaf(lam, S[4 * i + 1], k4.y * v);
-        S[4 * i + 2] = fmaf(lam, S[4 * i + 2], k4.z * v);
-        S[4 * i + 3] = fmaf(lam, S[4 * i + 3], k4.w * v);
-        a0 = fmaf(S[4 * i], q4.x, a0);
-        a1 = fmaf(S[4 * i + 1], q4.y, a1);
-        a2 = fmaf(S[4 * i + 2], q4.z, a2);
-        a3 = fmaf(S[4 * i + 3], q4.w, a3);
+        S0[4 * i] = fmaf(lam, S0[4 * i], k4.x * v.x);
+        S0[4 * i + 1] = fmaf(lam, S0[4 * i + 1], k4.y * v.x);
+        S0[4 * i + 2] = fmaf(lam, S0[4 * i + 2], k4.z * v.x);
+        S0[4 * i + 3] = fmaf(lam, S0[4 * i + 3], k4.w * v.x);
+        S1[4 * i] = fmaf(lam, S1[4 * i], k4.x * v.y);
+        S1[4 * i + 1] = fmaf(lam, S1[4 * i + 1], k4.y * v.y);
+        S1[4 * i + 2] = fmaf(lam, S1[4 * i + 2], k4.z * v.y);
+        S1[4 * i + 3] = fmaf(lam, S1[4 * i + 3], k4.w * v.y);
+        a0 = fmaf(S0[4 * i], q4.x, a0);
+        a1 = fmaf(S0[4 * i + 1], q4.y, a1);
+        a2 = fmaf(S0[4 * i + 2], q4.z, a2);
+        a3 = fmaf(S0[4 * i + 3], q4.w, a3);
+        b0 = fmaf(S1[4 * i], q4.x, b0);
+        b1 = fmaf(S1[4 * i + 1], q4.y, b1);
+        b2 = fmaf(S1[4 * i + 2], q4.z, b2);
+        b3 = fmaf(S1[4 * i + 3], q4.w, b3);
       }
       if (phase != LOCAL) {
-        float acc = (a0 + a1) + (a2 + a3);
+        float acc0 = (a0 + a1) + (a2 + a3), acc1 = (b0 + b1) + (b2 + b3);
         // the four parts of a column are neighbouring lanes: part 0 + 1, 2 + 3, then the two sums
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        if (part == 0 && j < e) out[(size_t)(c0 + tt) * H * e + (size_t)h * e + j] = acc;
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        if (part == 0) {
+          float* orow = out + (size_t)(c0 + tt) * H * e + (size_t)h * e;
+          if (j0 < e) orow[j0] = acc0;
+          if (j1 < e) orow[j1] = acc1;
+        }
       }
     }
   }
@@ -114,7 +129,8 @@ __global__ void __launch_bounds__(EB * PARTS) lightning_scan_kernel(
 #pragma unroll
   for (int i = 0; i < RMAX; ++i) {
     const int r = part * RMAX + i;
-    if (r < d && j < e) dst[(size_t)r * e + j] = S[i];
+    if (r < d && j0 < e) dst[(size_t)r * e + j0] = S0[i];
+    if (r < d && j1 < e) dst[(size_t)r * e + j1] = S1[i];
   }
 }
 
@@ -182,7 +198,7 @@ JB_EXPORT int jb_lightning_scan(const float* proj, int ld, int q_col, int k_col,
   const int seg = segmented ? seg_len : 0x40000000;
 #define JB_LAUNCH_LS(RM, PHASE)                                                                                      \
   do {                                                                                                               \
-    jb::Launch cfg(dim3(n_seqs * tiles, H, (e + EB - 1) / EB), dim3(EB * PARTS), smem, stream);                     \
+    jb::Launch cfg(dim3(n_seqs * tiles, H, (e + EB - 1) / EB), dim3(EB / 2 * PARTS), smem, stream);                     \
     cudaError_t err = cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<RM>, proj, ld, q_col, k_col, v_col, out,     \
                                          state, q_start, seq_slot, decay, H, d, e, seg, tiles, scratch, (int)PHASE); \
     if (err != cudaSuccess) return (int)err;                                                                         \
