@@ -147,6 +147,10 @@ __global__ void __launch_bounds__(128) diff_prefill_kernel(
     const int b = it < n_sink ? it : blk_lo + it - n_sink;
     const int key0 = b * PAGE;
     const bf16* vs = Vs + (size_t)stage * PAGE * VLD;
+    // a page that every row of the warp sees whole needs no mask
+    const int w_lo = p_lo + (warp * 16) / R, w_hi = p_lo + min((warp * 16 + 15) / R, n_tok - 1);
+    const bool whole = (warp * 16 + 15) / R < n_tok && key0 + PAGE - 1 <= w_lo && (window <= 0 || w_hi - key0 < window);
+    unsigned P[2][PAGE / 8][2];
 #pragma unroll
     for (int mp = 0; mp < 2; ++mp) {
       const bf16* ks = Ks + ((size_t)stage * 2 + mp) * PAGE * KLD;
@@ -173,7 +177,7 @@ __global__ void __launch_bounds__(128) diff_prefill_kernel(
         for (int i = 0; i < 4; ++i) {
           const int key = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
           const int pos = i < 2 ? pos0 : pos1;
-          const bool seen = key <= pos && (window <= 0 || pos - key < window || key < keep_first);
+          const bool seen = whole || (key <= pos && (window <= 0 || pos - key < window || key < keep_first));
           S[nt][i] = seen ? S[nt][i] * scale_log2 : -CUDART_INF_F;
         }
         mx0 = fmaxf(mx0, fmaxf(S[nt][0], S[nt][1]));
@@ -189,15 +193,14 @@ __global__ void __launch_bounds__(128) diff_prefill_kernel(
       m[mp][0] = n0;
       m[mp][1] = n1;
       float s0 = 0.0f, s1 = 0.0f;
-      unsigned P[PAGE / 8][2];
 #pragma unroll
       for (int nt = 0; nt < PAGE / 8; ++nt) {
         const float p0 = exp2f(S[nt][0] - u0), p1 = exp2f(S[nt][1] - u0);
         const float p2 = exp2f(S[nt][2] - u1), p3 = exp2f(S[nt][3] - u1);
         s0 += p0 + p1;
         s1 += p2 + p3;
-        P[nt][0] = pack_bf16(p0, p1);
-        P[nt][1] = pack_bf16(p2, p3);
+        P[mp][nt][0] = pack_bf16(p0, p1);
+        P[mp][nt][1] = pack_bf16(p2, p3);
       }
       l[mp][0] = l[mp][0] * al0 + s0;
       l[mp][1] = l[mp][1] * al1 + s1;
@@ -208,14 +211,18 @@ __global__ void __launch_bounds__(128) diff_prefill_kernel(
         O[mp][nt][2] *= al1;
         O[mp][nt][3] *= al1;
       }
+    }
+    // both maps weigh the same values: a value tile is read from shared memory once for the two of them
 #pragma unroll
-      for (int kk = 0; kk < PAGE / 16; ++kk) {
+    for (int kk = 0; kk < PAGE / 16; ++kk) {
 #pragma unroll
-        for (int np = 0; np < E / 16; ++np) {
-          unsigned b0, b1, b2, b3;
-          ldmatrix_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + np * 16 + (lane >> 4) * 8);
-          mma_bf16(O[mp][2 * np], P[2 * kk][0], P[2 * kk][1], P[2 * kk + 1][0], P[2 * kk + 1][1], b0, b1);
-          mma_bf16(O[mp][2 * np + 1], P[2 * kk][0], P[2 * kk][1], P[2 * kk + 1][0], P[2 * kk + 1][1], b2, b3);
+      for (int np = 0; np < E / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + np * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int mp = 0; mp < 2; ++mp) {
+          mma_bf16(O[mp][2 * np], P[mp][2 * kk][0], P[mp][2 * kk][1], P[mp][2 * kk + 1][0], P[mp][2 * kk + 1][1], b0, b1);
+          mma_bf16(O[mp][2 * np + 1], P[mp][2 * kk][0], P[mp][2 * kk][1], P[mp][2 * kk + 1][0], P[mp][2 * kk + 1][1], b2, b3);
         }
       }
     }

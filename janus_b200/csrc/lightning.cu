@@ -31,6 +31,7 @@ typedef __nv_bfloat16 bf16;
 constexpr int PARTS = 4;      // threads that share a value column (each a quarter of the rows)
 constexpr int EB = 64;        // value columns a block owns, two a thread
 constexpr int CT = 16;        // tokens staged at a time
+constexpr int THREADS = EB / 2 * PARTS;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
@@ -73,15 +74,44 @@ __global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
   for (int c0 = t0; c0 < t1; c0 += CT) {
     const int n = min(CT, t1 - c0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * DP; idx += blockDim.x) {
-      const int tt = idx / DP, r = idx % DP;
-      const float* row = proj + (size_t)(c0 + tt) * ld;
-      q_s[idx] = r < d ? silu_f(row[q_col + h * d + r]) : 0.0f;
-      k_s[idx] = r < d ? silu_f(row[k_col + h * d + r]) : 0.0f;
+    // eight loads of each kind are in flight before their activations run (a load a time would leave the
+    // block waiting on memory for most of a chunk)
+    for (int base = 0; base < n * DP; base += 8 * THREADS) {
+      float qv[8], kv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * THREADS + threadIdx.x;
+        const int tt = idx / DP, r = idx % DP;
+        const bool in = idx < n * DP && r < d;
+        const float* row = proj + (size_t)(c0 + (in ? tt : 0)) * ld + h * d + (in ? r : 0);
+        qv[u] = in ? row[q_col] : 0.0f;
+        kv[u] = in ? row[k_col] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * THREADS + threadIdx.x;
+        if (idx < n * DP) {
+          const bool in = idx % DP < d;
+          q_s[idx] = in ? silu_f(qv[u]) : 0.0f;
+          k_s[idx] = in ? silu_f(kv[u]) : 0.0f;
+        }
+      }
     }
-    for (int idx = threadIdx.x; idx < n * EB; idx += blockDim.x) {
-      const int tt = idx / EB, c = idx % EB;
-      v_s[idx] = e0 + c < e ? silu_f(proj[(size_t)(c0 + tt) * ld + v_col + h * e + e0 + c]) : 0.0f;
+    {
+      float vv[CT * EB / THREADS];
+#pragma unroll
+      for (int u = 0; u < CT * EB / THREADS; ++u) {
+        const int idx = u * THREADS + threadIdx.x;
+        const int tt = idx / EB, c = idx % EB;
+        const bool in = tt < n && e0 + c < e;
+        vv[u] = in ? proj[(size_t)(c0 + tt) * ld + v_col + h * e + e0 + c] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < CT * EB / THREADS; ++u) {
+        const int idx = u * THREADS + threadIdx.x;
+        const int tt = idx / EB, c = idx % EB;
+        v_s[idx] = (tt < n && e0 + c < e) ? silu_f(vv[u]) : 0.0f;
+      }
     }
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
