@@ -100,6 +100,95 @@ __global__ void conv_rope_cache_kernel(const float* __restrict__ proj, int ld, c
   }
 }
 
+// Four channels a thread (sizes and rotated dimensions that are multiples of 4 or 8, 16-byte aligned rows): the same
+// sums in the same order as the kernel above, with 16-byte loads of the projections and stores of q, and one set of
+// index arithmetic per four channels.
+template <typename TC>
+__device__ __forceinline__ void store4c(TC* p, float4 v);
+template <>
+__device__ __forceinline__ void store4c<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <>
+__device__ __forceinline__ void store4c<bf16>(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TC>
+__global__ void conv_rope_cache_vec_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w, int taps,
+                                           float* __restrict__ conv_state, int update_state, const int* __restrict__ token_seq,
+                                           const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                           const int* __restrict__ positions, const float* __restrict__ cos_sin, int rot,
+                                           float* __restrict__ q_out, const int* __restrict__ dest, TC* __restrict__ k_cache,
+                                           TC* __restrict__ v_cache, int H, int G, int d, int e, int page_size) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  const int Cq = H * 2 * d, Ck = G * 2 * d, Cv = G * e, C = Cq + Ck + Cv;
+  const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+  if (c >= C) return;
+  const int seq = token_seq[t];
+  const int local = t - q_start[seq];
+  float* st = (conv_w && taps > 1) ? conv_state + (size_t)seq_slot[seq] * (taps - 1) * C : nullptr;
+  const int half = rot >> 1;
+  const float* cs = cos_sin ? cos_sin + (size_t)positions[t] * half * 2 : nullptr;
+  const int dst = dest[t];
+  const int page = dst / page_size, off = dst % page_size;
+
+  auto convolved = [&](int c0) -> float4 {
+    if (!conv_w) return *reinterpret_cast<const float4*>(proj + (size_t)t * ld + c0);
+    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;
+      const float4 u = back <= local ? *reinterpret_cast<const float4*>(proj + (size_t)(t - back) * ld + c0)
+                                     : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 - (back - local)) * C + c0);
+      const float* w = conv_w + (size_t)c0 * taps + j;
+      y.x = fmaf(w[0], u.x, y.x);
+      y.y = fmaf(w[taps], u.y, y.y);
+      y.z = fmaf(w[2 * taps], u.z, y.z);
+      y.w = fmaf(w[3 * taps], u.w, y.w);
+    }
+    return y;
+  };
+  auto put = [&](int c0, float4 y) {
+    if (c0 < Cq) {
+      *reinterpret_cast<float4*>(q_out + (size_t)t * Cq + c0) = y;
+    } else if (c0 < Cq + Ck) {
+      const int kc = c0 - Cq, vec = kc / d, i = kc % d;
+      store4c<TC>(k_cache + (((size_t)page * 2 * G + vec) * page_size + off) * d + i, y);
+    } else {
+      const int vc = c0 - Cq - Ck, g = vc / e, i = vc % e;
+      store4c<TC>(v_cache + (((size_t)page * G + g) * page_size + off) * e + i, y);
+    }
+  };
+  auto shift = [&](int c0) {
+    if (!update_state || st == nullptr) return;
+    for (int i = 0; i + 1 < taps - 1; ++i)
+      *reinterpret_cast<float4*>(st + (size_t)i * C + c0) = *reinterpret_cast<const float4*>(st + (size_t)(i + 1) * C + c0);
+    *reinterpret_cast<float4*>(st + (size_t)(taps - 2) * C + c0) = *reinterpret_cast<const float4*>(proj + (size_t)t * ld + c0);
+  };
+  if (c >= Cq + Ck || cs == nullptr) {
+    put(c, convolved(c));
+    shift(c);
+    return;
+  }
+  const int i = (c < Cq ? c : c - Cq) % d;
+  if (i >= rot) {
+    put(c, convolved(c));
+    shift(c);
+  } else if (i < half) {
+    const float4 a = convolved(c), b = convolved(c + half);
+    const float4 t0 = *reinterpret_cast<const float4*>(cs + 2 * i), t1 = *reinterpret_cast<const float4*>(cs + 2 * i + 4);
+    // (cos, sin) of the pairs i, i + 1 in t0 and of i + 2, i + 3 in t1
+    put(c, make_float4(a.x * t0.x - b.x * t0.y, a.y * t0.z - b.y * t0.w, a.z * t1.x - b.z * t1.y, a.w * t1.z - b.w * t1.w));
+    put(c + half, make_float4(b.x * t0.x + a.x * t0.y, b.y * t0.z + a.y * t0.w, b.z * t1.x + a.z * t1.y, b.w * t1.z + a.w * t1.w));
+    shift(c);
+    shift(c + half);
+  }
+}
+
 __global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld, float* __restrict__ conv_state, int taps,
                                          const int* __restrict__ q_start, const int* __restrict__ seq_slot, int C) {
   jb::pdl_launch_dependents();
@@ -335,6 +424,22 @@ JB_EXPORT int jb_conv_rope_cache(const float* proj, int ld, const float* conv_w,
   JB_REFUSE(conv_w != nullptr && taps < 1, "conv_rope_cache: %d taps", taps);
   const int C = H * 2 * d + G * 2 * d + G * e;
   const int threads = C >= 1024 ? 256 : 128;
+  const bool vec = d % 4 == 0 && e % 4 == 0 && rot % 8 == 0 && ld % 4 == 0 &&
+                   (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)conv_state |
+                     (uintptr_t)cos_sin) & 15) == 0;
+  if (vec) {
+    const int vthreads = C / 4 >= 512 ? 256 : 128;
+    jb::Launch vcfg(dim3(T, (C / 4 + vthreads - 1) / vthreads), dim3(vthreads), 0, stream);
+    if (cache_dtype == JB_F32)
+      return (int)cudaLaunchKernelEx(&vcfg.c, conv_rope_cache_vec_kernel<float>, proj, ld, conv_w, taps, conv_state,
+                                     update_state, token_seq, q_start, seq_slot, positions, cos_sin, rot, q_out, dest,
+                                     (float*)k_cache, (float*)v_cache, H, G, d, e, page_size);
+    if (cache_dtype == JB_BF16)
+      return (int)cudaLaunchKernelEx(&vcfg.c, conv_rope_cache_vec_kernel<bf16>, proj, ld, conv_w, taps, conv_state,
+                                     update_state, token_seq, q_start, seq_slot, positions, cos_sin, rot, q_out, dest,
+                                     (bf16*)k_cache, (bf16*)v_cache, H, G, d, e, page_size);
+    return JB_ERR_BAD_DTYPE;
+  }
   jb::Launch cfg(dim3(T, (C + threads - 1) / threads), dim3(threads), 0, stream);
   if (cache_dtype == JB_F32)
     return (int)cudaLaunchKernelEx(&cfg.c, conv_rope_cache_kernel<float>, proj, ld, conv_w, taps, conv_state, update_state, token_seq,

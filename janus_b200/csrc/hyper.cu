@@ -21,14 +21,24 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int MAX_STREAMS = 8;
 
+// A read can also clear a scratch buffer of the sublayer that runs next (the target of a product whose slices of K
+// meet by atomic adds): each block clears its share.
+__device__ __forceinline__ void clear_slice(float4* __restrict__ p, size_t n4) {
+  if (p == nullptr) return;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
+    p[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+}
+
 template <typename TG, typename TO>
 __global__ void streams_rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
                                        const float* __restrict__ a, int S, const TG* __restrict__ gamma, float eps,
-                                       TO* __restrict__ out, int H, float* __restrict__ clear) {
-  extern __shared__ float u_s[];          // H floats, then 33 of scratch
+                                       TO* __restrict__ out, int H, float* __restrict__ clear,
+                                       float4* __restrict__ clear2, size_t clear2_n4) {
+  extern __shared__ __align__(16) float u_s[];          // H floats, then 33 of scratch
   float* scratch = u_s + H;
   jb::pdl_launch_dependents();
   jb::pdl_wait();
+  clear_slice(clear2, clear2_n4);
   const int r = blockIdx.x;
   const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
   const float* xr = x + src * (size_t)S * H;
@@ -57,8 +67,9 @@ __global__ void streams_rmsnorm_kernel(const float* __restrict__ x, const int* _
 template <typename TG, typename TO>
 __global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ M,
                                            const float* __restrict__ b, const float* __restrict__ a, int S,
-                                           const TG* __restrict__ gamma, float eps, TO* __restrict__ out, int H) {
-  extern __shared__ float u_s[];          // H floats, then 33 of scratch, then M, b, a
+                                           const TG* __restrict__ gamma, float eps, TO* __restrict__ out, int H,
+                                           float4* __restrict__ clear2, size_t clear2_n4) {
+  extern __shared__ __align__(16) float u_s[];          // H floats, then 33 of scratch, then M, b, a
   float* scratch = u_s + H;
   float* m_s = scratch + 33;
   if (threadIdx.x < S * S) m_s[threadIdx.x] = M[threadIdx.x];
@@ -68,10 +79,46 @@ __global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, float* __restr
   }
   jb::pdl_launch_dependents();
   jb::pdl_wait();
+  clear_slice(clear2, clear2_n4);
   __syncthreads();
   const int r = blockIdx.x;
   float* xr = x + (size_t)r * S * H;
   float ss = 0.0f;
+  if ((H & 3) == 0) {
+    // four columns a thread: 16-byte loads and stores of the streams, the same sums per column
+    float4* yr = reinterpret_cast<float4*>(y + (size_t)r * H);
+    for (int i4 = threadIdx.x; i4 < (H >> 2); i4 += blockDim.x) {
+      float4 old[MAX_STREAMS];
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        old[s] = s < S ? *reinterpret_cast<const float4*>(xr + (size_t)s * H + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 yv = yr[i4];
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int to = 0; to < MAX_STREAMS; ++to) {
+        if (to < S) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int s = 0; s < MAX_STREAMS; ++s)
+            if (s < S) {
+              const float m = m_s[s * S + to];
+              v.x = fmaf(m, old[s].x, v.x); v.y = fmaf(m, old[s].y, v.y);
+              v.z = fmaf(m, old[s].z, v.z); v.w = fmaf(m, old[s].w, v.w);
+            }
+          const float bo = m_s[MAX_STREAMS * MAX_STREAMS + to], an = m_s[MAX_STREAMS * MAX_STREAMS + MAX_STREAMS + to];
+          v.x = fmaf(bo, yv.x, v.x); v.y = fmaf(bo, yv.y, v.y); v.z = fmaf(bo, yv.z, v.z); v.w = fmaf(bo, yv.w, v.w);
+          *reinterpret_cast<float4*>(xr + (size_t)to * H + 4 * i4) = v;
+          u.x = fmaf(an, v.x, u.x); u.y = fmaf(an, v.y, u.y); u.z = fmaf(an, v.z, u.z); u.w = fmaf(an, v.w, u.w);
+        }
+      }
+      *reinterpret_cast<float4*>(u_s + 4 * i4) = u;
+      ss += u.x * u.x;
+      ss += u.y * u.y;
+      ss += u.z * u.z;
+      ss += u.w * u.w;
+      yr[i4] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  } else
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float old[MAX_STREAMS];
 #pragma unroll
@@ -133,11 +180,16 @@ __global__ void streams_mix_kernel(float* __restrict__ x, const float* __restric
 }  // namespace
 
 // x: float32 [*, S, H]; a: S float32 weights or null (plain sum); out: [rows, H] in out_dtype;
-// clear: null or a float32 [rows, H] buffer whose row r is set to zero (only without row_index).
+// clear: null or a float32 [rows, H] buffer whose row r is set to zero (only without row_index);
+// clear2: null or clear2_n floats (whole 16-byte vectors) that the launch sets to zero besides.
 JB_EXPORT int jb_streams_rmsnorm(const float* x, const int* row_index, const float* a, int S, const void* gamma,
                                  int gamma_dtype, float eps, void* out, int out_dtype, int rows, int H, float* clear,
-                                 cudaStream_t stream) {
+                                 float* clear2, long long clear2_n, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  JB_REFUSE(clear2 != nullptr && ((clear2_n & 3) != 0 || ((uintptr_t)clear2 & 15) != 0),
+            "streams_rmsnorm: the buffer to clear is not made of whole 16-byte vectors");
+  float4* clear2_4 = (float4*)clear2;
+  const size_t clear2_n4 = clear2 ? (size_t)clear2_n >> 2 : 0;
   JB_REFUSE(S < 1 || S > MAX_STREAMS, "streams_rmsnorm: %d streams are outside [1, %d]", S, MAX_STREAMS);
   JB_REFUSE(clear != nullptr && row_index != nullptr, "streams_rmsnorm: a buffer is cleared row by row only without a row index");
   const size_t smem = (size_t)(H + 33) * sizeof(float);
@@ -149,7 +201,7 @@ JB_EXPORT int jb_streams_rmsnorm(const float* x, const int* row_index, const flo
     if (smem > 48 * 1024)                                                                                       \
       cudaFuncSetAttribute(streams_rmsnorm_kernel<TG, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     e = cudaLaunchKernelEx(&cfg.c, streams_rmsnorm_kernel<TG, TO>, x, row_index, a, S, (const TG*)gamma, eps,   \
-                           (TO*)out, H, clear);                                                                 \
+                           (TO*)out, H, clear, clear2_4, clear2_n4);                                            \
   } while (0)
   if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_SN(float, float);
   else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_SN(float, bf16);
@@ -174,8 +226,12 @@ JB_EXPORT int jb_streams_mix(float* x, const float* y, const float* M, const flo
 // gamma and y[t] = 0, as jb_streams_rmsnorm with `clear` would do next.
 JB_EXPORT int jb_streams_mix_rmsnorm(float* x, float* y, const float* M, const float* b, const float* a, int S,
                                      const void* gamma, int gamma_dtype, float eps, void* out, int out_dtype, int T, int H,
-                                     cudaStream_t stream) {
+                                     float* clear2, long long clear2_n, cudaStream_t stream) {
   if (T <= 0) return 0;
+  JB_REFUSE(clear2 != nullptr && ((clear2_n & 3) != 0 || ((uintptr_t)clear2 & 15) != 0),
+            "streams_mix_rmsnorm: the buffer to clear is not made of whole 16-byte vectors");
+  float4* clear2_4 = (float4*)clear2;
+  const size_t clear2_n4 = clear2 ? (size_t)clear2_n >> 2 : 0;
   JB_REFUSE(S < 1 || S > MAX_STREAMS, "streams_mix_rmsnorm: %d streams are outside [1, %d]", S, MAX_STREAMS);
   const size_t smem = (size_t)(H + 33 + MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS) * sizeof(float);
   JB_REFUSE(smem > 200 * 1024, "streams_mix_rmsnorm: rows of %d floats do not fit shared memory", H);
@@ -186,7 +242,7 @@ JB_EXPORT int jb_streams_mix_rmsnorm(float* x, float* y, const float* M, const f
     if (smem > 48 * 1024)                                                                                           \
       cudaFuncSetAttribute(streams_mix_rmsnorm_kernel<TG, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     e = cudaLaunchKernelEx(&cfg.c, streams_mix_rmsnorm_kernel<TG, TO>, x, y, M, b, a, S, (const TG*)gamma, eps,     \
-                           (TO*)out, H);                                                                            \
+                           (TO*)out, H, clear2_4, clear2_n4);                                                       \
   } while (0)
   if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_SMN(float, float);
   else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_SMN(float, bf16);

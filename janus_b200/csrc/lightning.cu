@@ -38,12 +38,12 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 enum { WHOLE = 0, LOCAL = 1, FROM_START = 3 };
 
 // RMAX: rows of S a thread holds (a multiple of 4, 4 RMAX >= d); shared rows are padded to 4 RMAX with zeros
-template <int RMAX>
-__global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
+template <int RMAX, int PHASE>
+__global__ void __launch_bounds__(EB / 2 * PARTS, RMAX <= 32 ? 4 : 2) lightning_scan_kernel(
     const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, float* __restrict__ out,
     float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ seq_slot,
-    const float* __restrict__ decay, int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch,
-    int phase) {
+    const float* __restrict__ decay, int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch) {
+  constexpr int phase = PHASE;             // the pass from zero needs neither queries nor outputs
   constexpr int DP = PARTS * RMAX;         // padded rows
   extern __shared__ __align__(16) float smem[];          // q [CT][DP], k [CT][DP], v [CT][EB]
   float* q_s = smem;
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
         const int tt = idx / DP, r = idx % DP;
         const bool in = idx < n * DP && r < d;
         const float* row = proj + (size_t)(c0 + (in ? tt : 0)) * ld + h * d + (in ? r : 0);
-        qv[u] = in ? row[q_col] : 0.0f;
+        qv[u] = (in && phase != LOCAL) ? row[q_col] : 0.0f;
         kv[u] = in ? row[k_col] : 0.0f;
       }
 #pragma unroll
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
         const int idx = base + u * THREADS + threadIdx.x;
         if (idx < n * DP) {
           const bool in = idx % DP < d;
-          q_s[idx] = in ? silu_f(qv[u]) : 0.0f;
+          if (phase != LOCAL) q_s[idx] = in ? silu_f(qv[u]) : 0.0f;
           k_s[idx] = in ? silu_f(kv[u]) : 0.0f;
         }
       }
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
       float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
 #pragma unroll
       for (int i = 0; i < RMAX / 4; ++i) {
-        const float4 k4 = kr[i], q4 = qr[i];
+        const float4 k4 = kr[i];
         S0[4 * i] = fmaf(lam, S0[4 * i], k4.x * v.x);
         S0[4 * i + 1] = fmaf(lam, S0[4 * i + 1], k4.y * v.x);
         S0[4 * i + 2] = fmaf(lam, S0[4 * i + 2], k4.z * v.x);
@@ -130,14 +130,17 @@ __global__ void __launch_bounds__(EB / 2 * PARTS) lightning_scan_kernel(
         S1[4 * i + 1] = fmaf(lam, S1[4 * i + 1], k4.y * v.y);
         S1[4 * i + 2] = fmaf(lam, S1[4 * i + 2], k4.z * v.y);
         S1[4 * i + 3] = fmaf(lam, S1[4 * i + 3], k4.w * v.y);
-        a0 = fmaf(S0[4 * i], q4.x, a0);
-        a1 = fmaf(S0[4 * i + 1], q4.y, a1);
-        a2 = fmaf(S0[4 * i + 2], q4.z, a2);
-        a3 = fmaf(S0[4 * i + 3], q4.w, a3);
-        b0 = fmaf(S1[4 * i], q4.x, b0);
-        b1 = fmaf(S1[4 * i + 1], q4.y, b1);
-        b2 = fmaf(S1[4 * i + 2], q4.z, b2);
-        b3 = fmaf(S1[4 * i + 3], q4.w, b3);
+        if (phase != LOCAL) {
+          const float4 q4 = qr[i];
+          a0 = fmaf(S0[4 * i], q4.x, a0);
+          a1 = fmaf(S0[4 * i + 1], q4.y, a1);
+          a2 = fmaf(S0[4 * i + 2], q4.z, a2);
+          a3 = fmaf(S0[4 * i + 3], q4.w, a3);
+          b0 = fmaf(S1[4 * i], q4.x, b0);
+          b1 = fmaf(S1[4 * i + 1], q4.y, b1);
+          b2 = fmaf(S1[4 * i + 2], q4.z, b2);
+          b3 = fmaf(S1[4 * i + 3], q4.w, b3);
+        }
       }
       if (phase != LOCAL) {
         float acc0 = (a0 + a1) + (a2 + a3), acc1 = (b0 + b1) + (b2 + b3);
@@ -182,11 +185,19 @@ __global__ void lightning_prefix_kernel(float* __restrict__ scratch, const float
   float lam_seg = 1.0f;
   for (int i = 0; i < seg_len; ++i) lam_seg *= lam;          // the decay of a whole segment, as the walk applies it
   float S = state[(size_t)seq_slot[seq] * per + idx];
-  for (int seg = 0; seg < n_seg; ++seg) {
-    float* p = scratch + ((size_t)seq * tiles_per_seq + seg) * per + idx;
-    const float local = seg + 1 < n_seg ? *p : 0.0f;
-    *p = S;
-    S = fmaf(lam_seg, S, local);
+  float* p = scratch + (size_t)seq * tiles_per_seq * per + idx;
+  // four segments' states from zero are on their way before the first is used
+  for (int seg0 = 0; seg0 < n_seg; seg0 += 4) {
+    float local[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) local[u] = seg0 + u + 1 < n_seg ? p[(size_t)(seg0 + u) * per] : 0.0f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (seg0 + u < n_seg) {
+        p[(size_t)(seg0 + u) * per] = S;
+        S = fmaf(lam_seg, S, local[u]);
+      }
+    }
   }
 }
 
@@ -229,8 +240,8 @@ JB_EXPORT int jb_lightning_scan(const float* proj, int ld, int q_col, int k_col,
 #define JB_LAUNCH_LS(RM, PHASE)                                                                                      \
   do {                                                                                                               \
     jb::Launch cfg(dim3(n_seqs * tiles, H, (e + EB - 1) / EB), dim3(EB / 2 * PARTS), smem, stream);                     \
-    cudaError_t err = cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<RM>, proj, ld, q_col, k_col, v_col, out,     \
-                                         state, q_start, seq_slot, decay, H, d, e, seg, tiles, scratch, (int)PHASE); \
+    cudaError_t err = cudaLaunchKernelEx(&cfg.c, lightning_scan_kernel<RM, PHASE>, proj, ld, q_col, k_col, v_col,   \
+                                         out, state, q_start, seq_slot, decay, H, d, e, seg, tiles, scratch);        \
     if (err != cudaSuccess) return (int)err;                                                                         \
   } while (0)
 #define JB_LAUNCH_LS_R(PHASE)                       \

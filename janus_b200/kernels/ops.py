@@ -63,7 +63,7 @@ _SIGNATURES = {
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
     "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
-    "jb_streams_rmsnorm": "pppipifpiiipp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiip", "jb_embed_streams": "pippiiippp",
+    "jb_streams_rmsnorm": "pppipifpiiipplp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiiplp", "jb_embed_streams": "pippiiippp",
     "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
     "jb_conv_rope_cache": "pipipipppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
@@ -914,9 +914,10 @@ def embed_streams(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, str
 
 def streams_rmsnorm(x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], gamma: torch.Tensor, eps: float,
                     out: torch.Tensor, row_index: Optional[torch.Tensor] = None,
-                    clear: Optional[torch.Tensor] = None) -> None:
+                    clear: Optional[torch.Tensor] = None, clear2: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(sum_s weights[s] * x[row, s, :]) * gamma with x float32 [*, streams * H]; weights None:
-    the plain sum.  `clear`: a float32 [rows, H] tensor whose rows are set to zero by the same launch."""
+    the plain sum.  `clear`: a float32 [rows, H] tensor whose rows are set to zero by the same launch; `clear2`:
+    a float32 scratch tensor (whole 16-byte vectors) that it sets to zero besides."""
     rows, H = out.shape
     _need(x, "streams x", torch.float32)
     if x.dim() != 2 or x.shape[1] != streams * H:
@@ -933,7 +934,8 @@ def streams_rmsnorm(x: torch.Tensor, streams: int, weights: Optional[torch.Tenso
         _need(clear, "streams clear", torch.float32, (rows, H))
     _check(_lib("hyper").jb_streams_rmsnorm(
         _ptr(x), _ptr(row_index), _ptr(weights), int(streams), _ptr(gamma), dtype_code(gamma.dtype), eps, _ptr(out),
-        dtype_code(out.dtype), rows, H, _ptr(clear), _stream()), "streams_rmsnorm")
+        dtype_code(out.dtype), rows, H, _ptr(clear), _ptr(clear2), 0 if clear2 is None else clear2.numel(), _stream()),
+        "streams_rmsnorm")
 
 
 def streams_mix(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights: torch.Tensor, streams: int) -> None:
@@ -949,7 +951,7 @@ def streams_mix(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights
 
 def streams_mix_rmsnorm(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_weights: torch.Tensor,
                         next_weights: torch.Tensor, streams: int, gamma: torch.Tensor, eps: float,
-                        out: torch.Tensor) -> None:
+                        out: torch.Tensor, clear2: Optional[torch.Tensor] = None) -> None:
     """`streams_mix(x, y, mix, out_weights)` and then `streams_rmsnorm(x, next_weights, gamma) -> out` with y
     cleared, in one launch and with the same sums."""
     T, H = y.shape
@@ -962,7 +964,8 @@ def streams_mix_rmsnorm(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out
     _need(out, "streams out", None, (T, H))
     _check(_lib("hyper").jb_streams_mix_rmsnorm(
         _ptr(x), _ptr(y), _ptr(mix), _ptr(out_weights), _ptr(next_weights), int(streams), _ptr(gamma),
-        dtype_code(gamma.dtype), eps, _ptr(out), dtype_code(out.dtype), T, H, _stream()), "streams_mix_rmsnorm")
+        dtype_code(gamma.dtype), eps, _ptr(out), dtype_code(out.dtype), T, H, _ptr(clear2),
+        0 if clear2 is None else clear2.numel(), _stream()), "streams_mix_rmsnorm")
 
 
 # -- linear attention with decay ----------------------------------------------------------

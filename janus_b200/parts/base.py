@@ -225,10 +225,11 @@ class Norm(Part):
         raise NotImplementedError
 
     def forward_streams(self, x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], out: torch.Tensor,
-                        row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+                        row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None,
+                        clear2: Optional[torch.Tensor] = None) -> None:
         """The norm of sum_s weights[s] * x[:, s] for x float32 [rows, streams * width] (weights None: the plain
-        sum); `clear`: a float32 [rows, width] tensor set to zero by the same launch.  Needed only by models with
-        several residual streams."""
+        sum); `clear`: a float32 [rows, width] tensor set to zero by the same launch, `clear2`: a float32 scratch
+        tensor of the part that runs next, zeroed besides.  Needed only by models with several residual streams."""
         raise NotImplementedError
 
 
@@ -256,7 +257,8 @@ class FeedForward(Part):
 class Connection(Part):
     """How a sublayer meets a residual of several streams."""
 
-    def read(self, residual: torch.Tensor, norm: "Norm", out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> None:
+    def read(self, residual: torch.Tensor, norm: "Norm", out: torch.Tensor, clear: Optional[torch.Tensor] = None,
+             clear2: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 
     def write(self, residual: torch.Tensor, y: torch.Tensor) -> None:

@@ -76,13 +76,19 @@ class HyperConnectedBlock:
         # runs in the same launch; the model flushes the last one before its final norm
         pending = ctx.pending_write
         ctx.pending_write = None
+        # a mixer may name a scratch buffer that it wants zeroed; the read before it does that in passing
+        wants = getattr(self.mixer, "scratch_to_clear", None)
+        scratch = wants(ctx, T, writes_cache) if wants is not None else None
         if pending is not None and pending[1] is y and hasattr(pending[0], "write_then_read"):
-            pending[0].write_then_read(residual, y, self.mixer_connection, self.mixer_norm, x)
+            pending[0].write_then_read(residual, y, self.mixer_connection, self.mixer_norm, x, clear2=scratch)
         else:
             if pending is not None:
                 pending[0].write(residual, pending[1])
-            self.mixer_connection.read(residual, self.mixer_norm, x, clear=y)
-        self.mixer.forward(x, y, ctx, cache_view, writes_cache)
+            self.mixer_connection.read(residual, self.mixer_norm, x, clear=y, clear2=scratch)
+        if scratch is not None:
+            self.mixer.forward(x, y, ctx, cache_view, writes_cache, scratch_cleared=True)
+        else:
+            self.mixer.forward(x, y, ctx, cache_view, writes_cache)
         last = self.mixer_connection
         if self.feed_forward is not None:
             if hasattr(last, "write_then_read"):

@@ -39,23 +39,25 @@ class HyperConnection(Connection):
         self.b = out.to(device=self.device, dtype=torch.float32).contiguous()
         self.mix = mix.to(device=self.device, dtype=torch.float32).contiguous()
 
-    def read(self, residual: torch.Tensor, norm, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> None:
-        """out = norm(sum_s a[s] x_s); `clear` ([T, width] float32, the sublayer's target) is zeroed on the way."""
-        norm.forward_streams(residual, self.streams, self.a, out, clear=clear)
+    def read(self, residual: torch.Tensor, norm, out: torch.Tensor, clear: Optional[torch.Tensor] = None,
+             clear2: Optional[torch.Tensor] = None) -> None:
+        """out = norm(sum_s a[s] x_s); `clear` ([T, width] float32, the sublayer's target) is zeroed on the way, and
+        `clear2` (a scratch tensor that the sublayer wants zeroed) too."""
+        norm.forward_streams(residual, self.streams, self.a, out, clear=clear, clear2=clear2)
 
     def write(self, residual: torch.Tensor, y: torch.Tensor) -> None:
         ops.streams_mix(residual, y, self.mix, self.b, self.streams)
 
     def write_then_read(self, residual: torch.Tensor, y: torch.Tensor, then: "HyperConnection", norm,
-                        out: torch.Tensor) -> None:
+                        out: torch.Tensor, clear2: Optional[torch.Tensor] = None) -> None:
         """This sublayer's write and the next sublayer's read (`then`, with its norm) in one launch; y is
         left zeroed for the next sublayer to add into."""
         gamma, eps = getattr(norm, "gamma", None), getattr(norm, "eps", None)
         if isinstance(then, HyperConnection) and then.streams == self.streams and gamma is not None and eps is not None:
-            ops.streams_mix_rmsnorm(residual, y, self.mix, self.b, then.a, self.streams, gamma, eps, out)
+            ops.streams_mix_rmsnorm(residual, y, self.mix, self.b, then.a, self.streams, gamma, eps, out, clear2)
         else:
             self.write(residual, y)
-            then.read(residual, norm, out, clear=y)
+            then.read(residual, norm, out, clear=y, clear2=clear2)
 
 
 register_part("connection", "hyper_connection", HyperConnection)

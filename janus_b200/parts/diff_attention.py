@@ -87,14 +87,23 @@ class DifferentialAttention(Mixer):
                 raise ValueError(f"convolution weights of shape {tuple(w.shape)} do not fit ({self.channels}, {self.taps})")
             self.conv_weight = w.to(self.device).contiguous()
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+    def scratch_to_clear(self, ctx, tokens: int, writes_cache: bool = True) -> Optional[torch.Tensor]:
+        """The projections' float32 buffer, if this step's product adds slices of K into it (decode-sized steps):
+        the read before this mixer clears it in the same launch."""
+        if not self.qkv.meets_by_adds(tokens, torch.float32):
+            return None
+        buf = ctx.workspace.get("diff_qkv", (tokens, self.channels), torch.float32)
+        return buf if buf.numel() % 4 == 0 else None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True,
+                scratch_cleared: bool = False) -> None:
         if not writes_cache:
             raise ValueError("differential attention writes its own keys and values; it cannot read another place's")
         T = x.shape[0]
         ws = ctx.workspace
         group = cache_view.group
         proj = ws.get("diff_qkv", (T, self.channels), torch.float32)
-        self.qkv.forward(x, proj)
+        self.qkv.forward(x, proj, y_is_zero=scratch_cleared)
         table = self.position.fused_rotary_table() if self.position is not None else None
         q = ws.get("diff_q", (T, self.q_width), torch.float32)
         ops.conv_rope_cache(proj, self.conv_weight, self.taps, cache_view.state if self.taps > 1 else None,

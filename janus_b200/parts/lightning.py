@@ -54,13 +54,22 @@ class LightningAttention(Mixer):
             norm = norm.to(torch.float32)
         self.norm_weight = norm.to(self.device).contiguous()
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+    def scratch_to_clear(self, ctx, tokens: int, writes_cache: bool = True) -> Optional[torch.Tensor]:
+        """The projections' float32 buffer, if this step's product adds slices of K into it (decode-sized steps):
+        the read before this mixer clears it in the same launch."""
+        if not self.proj.meets_by_adds(tokens, torch.float32):
+            return None
+        buf = ctx.workspace.get("lightning_proj", (tokens, self.proj.out_features), torch.float32)
+        return buf if buf.numel() % 4 == 0 else None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True,
+                scratch_cleared: bool = False) -> None:
         if not writes_cache:
             raise ValueError("a lightning mixer cannot read another place's state: its state is its own")
         T = x.shape[0]
         ws = ctx.workspace
         proj = ws.get("lightning_proj", (T, self.proj.out_features), torch.float32)
-        self.proj.forward(x, proj)
+        self.proj.forward(x, proj, y_is_zero=scratch_cleared)
         o = ws.get("lightning_o", (T, self.v_width), torch.float32)
         ops.lightning_scan(proj, 0, self.qk_width, 2 * self.qk_width, o, cache_view.state, ctx.q_start, ctx.seq_slot,
                            self.decay, ctx.n_seqs, self.nh, self.dim, self.vdim, ctx.max_q_len, ws)

@@ -34,9 +34,10 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.gamma, self.eps, out, row_index, clear)
 
     def forward_streams(self, x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], out: torch.Tensor,
-                        row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+                        row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None,
+                        clear2: Optional[torch.Tensor] = None) -> None:
         """The norm of the weighted sum of `streams` residual streams, summed and normed in one launch."""
-        ops.streams_rmsnorm(x, streams, weights, self.gamma, self.eps, out, row_index, clear)
+        ops.streams_rmsnorm(x, streams, weights, self.gamma, self.eps, out, row_index, clear, clear2)
 
 
 register_part("norm", "rms_norm", RMSNorm)
