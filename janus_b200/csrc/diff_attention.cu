@@ -204,7 +204,9 @@ __global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld,
   }
 }
 
-constexpr int MAX_WARPS = 8;
+// warps of a block at most, by the value columns a lane holds (a block of 32 warps leaves a thread 64 registers,
+// which the kernel for up to 64 value columns fits into)
+__host__ __device__ constexpr int max_warps(int ej) { return ej <= 2 ? 32 : 16; }
 
 // dot products of one key's two maps with the query's two maps, 8 (bf16) or 4 (float) elements a load when
 // the rows allow it
@@ -258,11 +260,60 @@ __device__ __forceinline__ void dot2<bf16>(const float* __restrict__ qw, const b
   }
 }
 
+// A lane's EJ neighbouring value columns of one row, in one load when the row's length is a multiple of EJ
+template <int EJ>
+__device__ __forceinline__ void load_columns_f32(const float* __restrict__ vr, int c0, int e, bool vec, float (&v)[EJ]) {
+  if (vec && c0 < e) {
+    if (EJ == 2) {
+      const float2 t = *reinterpret_cast<const float2*>(vr + c0);
+      v[0] = t.x; v[1] = t.y;
+    } else {
+#pragma unroll
+      for (int j = 0; j < EJ; j += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(vr + c0 + j);
+        v[j] = t.x; v[j + 1] = t.y; v[j + 2] = t.z; v[j + 3] = t.w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) v[j] = c0 + j < e ? vr[c0 + j] : 0.0f;
+  }
+}
+template <int EJ>
+__device__ __forceinline__ void load_columns_bf16(const bf16* __restrict__ vr, int c0, int e, bool vec, float (&v)[EJ]) {
+  if (vec && c0 < e) {
+    unsigned raw[EJ / 2];
+    if (EJ == 2) raw[0] = *reinterpret_cast<const unsigned*>(vr + c0);
+    else if (EJ == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(vr + c0);
+    else *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(vr + c0);
+#pragma unroll
+    for (int j = 0; j < EJ / 2; ++j) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[j]));
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) v[j] = c0 + j < e ? __bfloat162float(vr[c0 + j]) : 0.0f;
+  }
+}
+template <typename TC, int EJ> struct Columns;
+template <int EJ> struct Columns<float, EJ> {
+  static __device__ __forceinline__ void load(const float* vr, int c0, int e, bool vec, float (&v)[EJ]) {
+    load_columns_f32<EJ>(vr, c0, e, vec, v);
+  }
+};
+template <int EJ> struct Columns<bf16, EJ> {
+  static __device__ __forceinline__ void load(const bf16* vr, int c0, int e, bool vec, float (&v)[EJ]) {
+    load_columns_bf16<EJ>(vr, c0, e, vec, v);
+  }
+};
+
 // One block per (token, query head); its warps take the chunks of 32 keys in turn (chunk n goes to warp
 // n mod warps) and their partial results (maximum, sum, weighted values of each map) meet in warp order.
-// EJ: value columns a lane holds (e <= 32 EJ)
+// EJ: value columns a lane holds, EJ lane .. EJ lane + EJ - 1 (e <= 32 EJ)
 template <typename TC, typename TO, int EJ>
-__global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
+__global__ void __launch_bounds__(max_warps(EJ) * 32) diff_attention_kernel(
     const float* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, TO* __restrict__ out,
     const int* __restrict__ block_table, const int* __restrict__ token_seq, const int* __restrict__ positions, int T, int H,
     int G, int d, int e, int page_size, int max_pages, int window, int keep_first, float scale, float lambda, float eps,
@@ -276,6 +327,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
   const int pos = positions[t];
   const int* pages = block_table + (size_t)token_seq[t] * max_pages;
   const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const bool vvec = (vec & 2) != 0 && e % EJ == 0;         // a lane's EJ neighbouring value columns come in one load
   float* qw = smem;
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) qw[i] = q[((size_t)t * H + h) * 2 * d + i];
   __syncthreads();
@@ -293,7 +345,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
       const int page = pages[key / page_size], row = key % page_size;
       const TC* k1 = k_cache + (((size_t)page * 2 * G + 2 * g) * page_size + row) * d;
       float d1, d2;
-      dot2<TC>(qw, k1, k1 + (size_t)page_size * d, d, vec != 0, d1, d2);
+      dot2<TC>(qw, k1, k1 + (size_t)page_size * d, d, (vec & 1) != 0, d1, d2);
       s1 = d1 * scale;
       s2 = d2 * scale;
     }
@@ -320,11 +372,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const TC* vr = vbase + (size_t)(kk0 + u) * e;
-#pragma unroll
-          for (int j = 0; j < EJ; ++j) {
-            const int c = lane + 32 * j;
-            vreg[u][j] = c < e ? jb::to_f32(vr[c]) : 0.0f;
-          }
+          Columns<TC, EJ>::load(vr, EJ * lane, e, vvec, vreg[u]);
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -345,7 +393,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
         const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
 #pragma unroll
         for (int j = 0; j < EJ; ++j) {
-          const int c = lane + 32 * j;
+          const int c = EJ * lane + j;
           if (c < e) {
             const float v = jb::to_f32(vr[c]);
             a1[j] = fmaf(w1, v, a1[j]);
@@ -397,14 +445,14 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) diff_attention_kernel(
 #pragma unroll
   for (int j = 0; j < EJ; ++j) {
     o[j] = a1[j] / l1 - lambda * (a2[j] / l2);
-    if (lane + 32 * j < e) ss += o[j] * o[j];
+    if (EJ * lane + j < e) ss += o[j] * o[j];
   }
   ss = jb::warp_sum(ss);
   const float rms = sqrtf(ss / (float)e + eps);
   TO* orow = out + ((size_t)t * H + h) * e;
 #pragma unroll
   for (int j = 0; j < EJ; ++j) {
-    const int c = lane + 32 * j;
+    const int c = EJ * lane + j;
     if (c < e) orow[c] = jb::from_f32<TO>((o[j] / rms) * out_scale);
   }
 }
@@ -468,12 +516,19 @@ JB_EXPORT int jb_diff_attention(const float* q, const void* k_cache, const void*
   JB_REFUSE(G <= 0 || H % G != 0, "diff_attention: %d heads are not a multiple of %d key/value heads", H, G);
   JB_REFUSE(e < 1 || e > 256 || d < 1 || d > 1024, "diff_attention: sizes %d (keys) and %d (values) are not supported", d, e);
   JB_REFUSE((long long)T * H > 2147483647LL, "diff_attention: %d tokens of %d heads are too many blocks", T, H);
-  // few (token, head) pairs (single tokens): eight warps share a query's keys; prompts: four
-  const int warps = (long long)T * H <= 4096 ? MAX_WARPS : 4;
+  // few (token, head) pairs (single tokens): a warp per chunk of 32 keys a query can see, up to 32 warps, so that
+  // the chunks' loads are all in flight at once; prompts: four warps
   const int EJ_ = e <= 64 ? 2 : e <= 128 ? 4 : 8;
+  const long long reach = (long long)max_pages * page_size;
+  const long long keys = window > 0 ? (reach < (long long)window + keep_first ? reach : (long long)window + keep_first) : reach;
+  int warps = 4;
+  if ((long long)T * H <= 4096)
+    while (warps < max_warps(EJ_) && (long long)warps * 32 < keys) warps *= 2;
   const size_t smem = (size_t)(2 * d + warps * (4 + 64 * EJ_)) * sizeof(float);
   const bool f32c = cache_dtype == JB_F32;
-  const int vec = (d % (f32c ? 4 : 8) == 0) && (((uintptr_t)k_cache) & 15) == 0 ? 1 : 0;
+  // bit 0: key rows in 16-byte loads; bit 1: the value cache is aligned for a lane's columns in one load
+  const int vec = ((d % (f32c ? 4 : 8) == 0 && (((uintptr_t)k_cache) & 15) == 0) ? 1 : 0) |
+                  ((((uintptr_t)v_cache) & 15) == 0 ? 2 : 0);
   jb::Launch cfg(dim3((unsigned)(T * H)), dim3(warps * 32), smem, stream);
   cudaError_t err;
 #define JB_LAUNCH_DA(TC, TO, EJ)                                                                                     \
