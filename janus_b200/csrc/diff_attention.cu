@@ -309,6 +309,8 @@ template <int EJ> struct Columns<bf16, EJ> {
   }
 };
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // One block per (token, query head); its warps take the chunks of 32 keys in turn (chunk n goes to warp
 // n mod warps) and their partial results (maximum, sum, weighted values of each map) meet in warp order.
 // EJ: value columns a lane holds, EJ lane .. EJ lane + EJ - 1 (e <= 32 EJ)
@@ -327,6 +329,7 @@ __global__ void __launch_bounds__(max_warps(EJ) * 32) diff_attention_kernel(
   const int pos = positions[t];
   const int* pages = block_table + (size_t)token_seq[t] * max_pages;
   const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const bool prefetch = (vec & 4) != 0;
   const bool vvec = (vec & 2) != 0 && e % EJ == 0;         // a lane's EJ neighbouring value columns come in one load
   float* qw = smem;
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) qw[i] = q[((size_t)t * H + h) * 2 * d + i];
@@ -341,9 +344,26 @@ __global__ void __launch_bounds__(max_warps(EJ) * 32) diff_attention_kernel(
     const int key = c0 + lane;
     const bool valid = key <= pos && (key >= kstart || key < keep_first);
     float s1 = -CUDART_INF_F, s2 = -CUDART_INF_F;
+    if (prefetch) {
+      // what the warp reads next is asked for now: this key's value row (needed once the scores are known) and
+      // the two key rows of this lane's key in the warp's next chunk
+      const int nkey = key + 32 * warps;
+      if (nkey <= pos) {
+        const int npage = pages[nkey / page_size], nrow = nkey % page_size;
+        const char* nk = reinterpret_cast<const char*>(k_cache + (((size_t)npage * 2 * G + 2 * g) * page_size + nrow) * d);
+        for (int b = 0; b < d * (int)sizeof(TC); b += 128) {
+          prefetch_l2(nk + b);
+          prefetch_l2(nk + (size_t)page_size * d * sizeof(TC) + b);
+        }
+      }
+    }
     if (valid) {
       const int page = pages[key / page_size], row = key % page_size;
       const TC* k1 = k_cache + (((size_t)page * 2 * G + 2 * g) * page_size + row) * d;
+      if (prefetch) {
+        const char* vrow = reinterpret_cast<const char*>(v_cache + (((size_t)page * G + g) * page_size + row) * e);
+        for (int b = 0; b < e * (int)sizeof(TC); b += 128) prefetch_l2(vrow + b);
+      }
       float d1, d2;
       dot2<TC>(qw, k1, k1 + (size_t)page_size * d, d, (vec & 1) != 0, d1, d2);
       s1 = d1 * scale;
@@ -524,11 +544,27 @@ JB_EXPORT int jb_diff_attention(const float* q, const void* k_cache, const void*
   int warps = 4;
   if ((long long)T * H <= 4096)
     while (warps < max_warps(EJ_) && (long long)warps * 32 < keys) warps *= 2;
+  static int forced = -1;                  // JANUS_DIFF_WARPS: warps of a block whatever the shape (experiments)
+  if (forced < 0) {
+    const char* env = getenv("JANUS_DIFF_WARPS");
+    forced = env ? atoi(env) : 0;
+  }
+  if (forced > 0) warps = forced < max_warps(EJ_) ? forced : max_warps(EJ_);
   const size_t smem = (size_t)(2 * d + warps * (4 + 64 * EJ_)) * sizeof(float);
   const bool f32c = cache_dtype == JB_F32;
-  // bit 0: key rows in 16-byte loads; bit 1: the value cache is aligned for a lane's columns in one load
+  // bit 0: key rows in 16-byte loads; bit 1: the value cache is aligned for a lane's columns in one load; bit 2: prefetch
+  static int prefetch_on = -1;             // JANUS_DIFF_PREFETCH=0: no prefetch of the rows a warp reads next (experiments)
+  if (prefetch_on < 0) {
+    const char* env = getenv("JANUS_DIFF_PREFETCH");
+    prefetch_on = (env && env[0] == '0') ? 0 : 1;
+  }
+  static int vvec_on = -1;                 // JANUS_DIFF_VVEC=0: value columns by single loads (experiments)
+  if (vvec_on < 0) {
+    const char* env = getenv("JANUS_DIFF_VVEC");
+    vvec_on = (env && env[0] == '0') ? 0 : 1;
+  }
   const int vec = ((d % (f32c ? 4 : 8) == 0 && (((uintptr_t)k_cache) & 15) == 0) ? 1 : 0) |
-                  ((((uintptr_t)v_cache) & 15) == 0 ? 2 : 0);
+                  ((vvec_on && (((uintptr_t)v_cache) & 15) == 0) ? 2 : 0) | (prefetch_on ? 4 : 0);
   jb::Launch cfg(dim3((unsigned)(T * H)), dim3(warps * 32), smem, stream);
   cudaError_t err;
 #define JB_LAUNCH_DA(TC, TO, EJ)                                                                                     \
