@@ -541,9 +541,16 @@ JB_EXPORT int jb_diff_attention(const float* q, const void* k_cache, const void*
   const int EJ_ = e <= 64 ? 2 : e <= 128 ? 4 : 8;
   const long long reach = (long long)max_pages * page_size;
   const long long keys = window > 0 ? (reach < (long long)window + keep_first ? reach : (long long)window + keep_first) : reach;
+  // ... as long as all blocks still fit the SMs at once (a block's registers allow max_warps warps of them an SM)
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const long long room = (long long)sms * max_warps(EJ_);
   int warps = 4;
-  if ((long long)T * H <= 4096)
-    while (warps < max_warps(EJ_) && (long long)warps * 32 < keys) warps *= 2;
+  while (warps < max_warps(EJ_) && (long long)warps * 32 < keys && (long long)T * H * warps * 2 <= room) warps *= 2;
   static int forced = -1;                  // JANUS_DIFF_WARPS: warps of a block whatever the shape (experiments)
   if (forced < 0) {
     const char* env = getenv("JANUS_DIFF_WARPS");
