@@ -20,7 +20,8 @@ the bfloat16 model's logits are compared with those of the true 32-bit engine on
 the same weights (`checked`).
 
 Other modes (one JSON line per item, none of them the headline): --kernels,
---prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline, --float32.
+--prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline, --float32, --design
+(the Zivitar design beside the Llama decoder at equal layer sizes: prompt and decode throughput, a step's kernels).
 """
 import argparse
 import json

@@ -15,7 +15,8 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time; the cache adds room for the unused ends of "
+                         "their last pages (up to 64 live requests)")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch the kernels of single-token steps one by one instead of replaying them from "
                          "CUDA graphs, as generation does")
@@ -30,10 +31,11 @@ def main(argv=None) -> int:
     from janus_b200.engine.step import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    # every live request holds at least one page: as many slots as pages serve any trace that
-    # keeps within --max-tokens
-    model = janus_b200.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
-                            max_slots=max(1, (args.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE),
+    # --max-tokens counts tokens, the cache counts pages: a live request leaves up to a page less one token unused,
+    # so there is a page of slack for each of up to 64 live requests (no more requests than tokens).  Every live
+    # request holds at least one page: as many slots as pages serve any trace that keeps within --max-tokens.
+    pages = (max(args.max_tokens, 1) + PAGE_SIZE - 1) // PAGE_SIZE + min(max(args.max_tokens, 1), 64)
+    model = janus_b200.load(args.model, dtype=args.dtype, max_tokens=pages * PAGE_SIZE, max_slots=pages,
                             use_graphs=not args.no_graphs)
     slots: Dict[str, int] = {}
     for line in sys.stdin:
