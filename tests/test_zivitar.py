@@ -412,3 +412,31 @@ def test_the_replay_program_serves_the_design(tmp_path):
     got = np.concatenate([np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, CFG_C["vocab"]) for s in steps])
     ref = P.forward(CFG_C, w, ids)
     assert rel_err(got, ref[[0] + list(range(29, 40))]) < FP32_TOL
+
+
+@gpu
+def test_the_command_line_samples_from_the_design(tmp_path):
+    """`python -m janus_b200 DIR ...`: greedy tokens equal those of `generate`, and sampling with a temperature, top-k
+    and a seed runs through the device sampler; a folder with config.json alone runs with `--random-weights`."""
+    d, w = folder(tmp_path, CFG_D, 15)
+    base = [sys.executable, "-m", "janus_b200", d, "3,1,4,1,5", "9,2,6", "--max-tokens", "7", "--dtype", "float32", "--json"]
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([ROOT, os.environ.get("PYTHONPATH", "")]))
+    res = subprocess.run(base, capture_output=True, text=True, timeout=900, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    greedy = json.loads(res.stdout.strip().splitlines()[-1])["tokens"]
+    for p, o in zip(([3, 1, 4, 1, 5], [9, 2, 6]), greedy):
+        assert len(o) == 7
+        logits = P.forward(CFG_D, w, p + o)
+        assert all(int(logits[len(p) - 1 + j].argmax()) == tok for j, tok in enumerate(o))
+    res = subprocess.run(base + ["--temperature", "0.9", "--top-k", "12", "--top-p", "0.9", "--seed", "4"],
+                         capture_output=True, text=True, timeout=900, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    sampled = json.loads(res.stdout.strip().splitlines()[-1])["tokens"]
+    assert [len(o) for o in sampled] == [7, 7] and all(0 <= t < CFG_D["vocab"] for o in sampled for t in o)
+    only_config = tmp_path / "only_config"
+    only_config.mkdir()
+    (only_config / "config.json").write_text(json.dumps(CFG_A))
+    res = subprocess.run([sys.executable, "-m", "janus_b200", str(only_config), "1,2,3", "--max-tokens", "4", "--random-weights",
+                          "--json"], capture_output=True, text=True, timeout=900, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert len(json.loads(res.stdout.strip().splitlines()[-1])["tokens"][0]) == 4
