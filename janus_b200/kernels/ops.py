@@ -1091,6 +1091,7 @@ def diff_attention_prefill_supported(heads: int, kv_heads: int, dim: int, vdim: 
 
 
 _DIFF_MMA = os.environ.get("JANUS_DIFF_MMA", "1") != "0"     # 0: prompts attend on the CUDA-core kernel
+_DIFF_MMA_DEFINES = _defines_from_env("JANUS_DIFF_MMA_DEFINES")   # e.g. JB_DIFF_CTAS=1 (experiments)
 
 
 def diff_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -1107,7 +1108,7 @@ def diff_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     _need(block_table, "block table", torch.int32)
     _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
-    lib = _lib("diff_attention_mma", (int(dim), int(vdim)), lambda k: {"JB_DIFF_D": k[0], "JB_DIFF_E": k[1]})
+    lib = _lib("diff_attention_mma", (int(dim), int(vdim)), lambda k: dict({"JB_DIFF_D": k[0], "JB_DIFF_E": k[1]}, **_DIFF_MMA_DEFINES))
     _check(lib.jb_diff_attention_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len), n_seqs,
         max_q_len, heads, kv_heads, dim, vdim, page_size, block_table.shape[1], int(window), int(keep_first), scale, lam,
