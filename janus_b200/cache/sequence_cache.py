@@ -39,7 +39,9 @@ class KVGroup:
         shape = (n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
         v_shape = (n_pages, spec.v_heads, PAGE_SIZE, spec.v_dim)
         self.k: Dict[int, torch.Tensor] = {p: torch.zeros(shape, dtype=dtype, device=device) for p in self.places}
-        self.v: Dict[int, torch.Tensor] = {p: torch.zeros(v_shape, dtype=dtype, device=device) for p in self.places}
+        # a place whose values are its keys hands out the key pages for both
+        self.v: Dict[int, torch.Tensor] = self.k if spec.values_are_keys else {
+            p: torch.zeros(v_shape, dtype=dtype, device=device) for p in self.places}
         # pages[slot][i] holds keys [i*PAGE, (i+1)*PAGE); -1 once a window has passed it
         self.pages: List[List[int]] = [[] for _ in range(n_slots)]
 

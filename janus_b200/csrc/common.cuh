@@ -89,8 +89,10 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(x);
 }
 
-// The activation of a gated product, act(gate) * up.  limit <= 0: SiLU, gate * sigmoid(gate) * up.  limit > 0: the
-// clamped form g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+// The activation of a gated product, act(gate) * up.  limit == 0: SiLU, gate * sigmoid(gate) * up.  limit > 0: the
+// clamped form g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).  limit < 0: the
+// tanh form of GELU, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * up, written with
+// 0.5 (1 + tanh(a)) = 1 / (1 + exp(-2a)).
 struct Gate {
   float limit;
   float alpha;
@@ -100,6 +102,10 @@ __device__ __forceinline__ float gated(float g, float u, const Gate& gate) {
     g = fminf(g, gate.limit);
     u = fminf(fmaxf(u, -gate.limit), gate.limit) + 1.0f;
     return g * (1.0f / (1.0f + expf(-gate.alpha * g))) * u;
+  }
+  if (gate.limit < 0.0f) {
+    const float a = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return g * (1.0f / (1.0f + expf(-2.0f * a))) * u;
   }
   return g * (1.0f / (1.0f + expf(-g))) * u;
 }

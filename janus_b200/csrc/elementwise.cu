@@ -346,8 +346,9 @@ JB_EXPORT int jb_pack_weight_bf16(const void* src, int N, int K, void* dst, cuda
 }
 
 // ---------------------------------------------------------------------------
-// A gated activation with clamped branches: g = min(gate, limit), u = clamp(up, -limit, limit),
-// out = g * sigmoid(alpha g) * (u + 1).  gate_up: float32 rows of ld floats, the gate of feature c in
+// A gated activation behind a plain product, `jb::gated` with (limit, alpha): with clamped branches
+// (limit > 0: g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha g) * (u + 1)),
+// the tanh form of GELU times up (limit < 0), or SiLU times up (limit 0).  gate_up: float32 rows of ld floats, the gate of feature c in
 // column c, its up value in column up_col + c; out: [T, I] in out_dtype.
 // A scale and a soft cap on a float32 tensor in place: y = cap * tanh(x * scale / cap) (cap <= 0: y = x * scale).
 // ---------------------------------------------------------------------------
@@ -360,9 +361,7 @@ __global__ void clamped_glu_kernel(const float* __restrict__ gate_up, int ld, in
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const size_t t = i / I, c = i % I;
-  const float g = fminf(gate_up[t * ld + c], limit);
-  const float u = fminf(fmaxf(gate_up[t * ld + up_col + c], -limit), limit);
-  out[i] = jb::from_f32<TO>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+  out[i] = jb::from_f32<TO>(jb::gated(gate_up[t * ld + c], gate_up[t * ld + up_col + c], jb::Gate{limit, alpha}));
 }
 
 __global__ void scale_softcap_kernel(float* __restrict__ x, float scale, float cap, size_t n) {
@@ -415,4 +414,63 @@ JB_EXPORT int jb_pad_rows_bf16(const void* x, int K, void* out, int Kp, int T, c
   JB_REFUSE(Kp < K, "pad_rows: rows of %d do not hold %d", Kp, K);
   jb::Launch cfg(dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, pad_rows_bf16_kernel, (const bf16*)x, K, (bf16*)out, Kp, n);
+}
+
+// ---------------------------------------------------------------------------
+// A sublayer whose OUTPUT is normed before it joins the residual stream:
+//   residual[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * gamma      (y: the sublayer's float32 output, may be null)
+//   x_out[t] = residual[t] in the engine dtype                         (the next sublayer's input, may be null)
+//   y[t] = 0                                                           (the next sublayer adds its output into it)
+// One block per token; `clear` as in the norms.  With y null it only casts; with x_out null it only adds.
+// ---------------------------------------------------------------------------
+namespace {
+template <typename TG, typename TO>
+__global__ void sublayer_norm_add_kernel(float* __restrict__ y, const TG* __restrict__ gamma, float eps, float mult,
+                                         float* __restrict__ residual, TO* __restrict__ x_out, int H,
+                                         float4* __restrict__ clear, size_t clear_n4) {
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  clear_slice(clear, clear_n4);
+  const size_t row = (size_t)blockIdx.x * H;
+  float* res = residual + row;
+  if (y == nullptr) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) x_out[row + i] = jb::from_f32<TO>(res[i]);
+    return;
+  }
+  float* yr = y + row;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) ss += yr[i] * yr[i];
+  ss = jb::block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float r = res[i] + mult * ((yr[i] / rms) * jb::to_f32(gamma[i]));
+    res[i] = r;
+    yr[i] = 0.0f;
+    if (x_out != nullptr) x_out[row + i] = jb::from_f32<TO>(r);
+  }
+}
+}  // namespace
+
+JB_EXPORT int jb_sublayer_norm_add(float* y, const void* gamma, int gamma_dtype, float eps, float mult, float* residual,
+                                   void* x_out, int out_dtype, int T, int H, float* clear, long long clear_n,
+                                   cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(clear != nullptr && ((clear_n & 3) != 0 || ((uintptr_t)clear & 15) != 0),
+            "sublayer_norm_add: the buffer to clear is not made of whole 16-byte vectors");
+  JB_REFUSE(y == nullptr && x_out == nullptr, "sublayer_norm_add: nothing to do");
+  float4* clear4 = (float4*)clear;
+  const size_t clear_n4 = clear ? (size_t)clear_n >> 2 : 0;
+  jb::Launch cfg(dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream);
+  cudaError_t e;
+#define JB_LAUNCH_SN(TG, TO)                                                                                      \
+  e = cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_kernel<TG, TO>, y, (const TG*)gamma, eps, mult, residual,     \
+                         (TO*)x_out, H, clear4, clear_n4)
+  if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_SN(float, float);
+  else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_SN(float, bf16);
+  else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_SN(bf16, float);
+  else if (gamma_dtype == JB_BF16 && out_dtype == JB_BF16) JB_LAUNCH_SN(bf16, bf16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_SN
+  return (int)e;
 }

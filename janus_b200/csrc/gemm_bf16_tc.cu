@@ -623,7 +623,7 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
 // (`w_tiles` tiles of 16 KB in all; for mode SWIGLU the gate rows' tiles first and the up rows' tiles from row
 // tile `up_tile_offset` on); Y: [T, ldy] with N_out columns used.
 // mode: 0 store bf16, 1 store f32, 2 add into f32, 3 act(gate)*up -> bf16 (`jb::gated` with gate_limit, gate_alpha:
-// limit <= 0 is SiLU).
+// limit 0 is SiLU, limit < 0 the tanh form of GELU).
 // split_k > 1 only with mode 2: partial sums meet in Y through atomic adds, or, if `partials` (room for
 // `partial_floats` floats) and `tickets` (`n_tickets` ints, zero) are given, in the fixed order of the slices:
 // tiles x slices x 128 x token tile floats and one ticket per output tile are needed (token tile: 16, 32, 64,

@@ -590,7 +590,7 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
 // cuts K of an adding product (mode ADD_F32) into that many slices, which meet in Y by atomic adds; the first
 // `whole_tiles` output tiles (256 x 256, token tile fastest) stay uncut: the tiles that fill whole waves of CTA
 // pairs, so that only the last, partial wave is cut.
-// Mode SWIGLU applies `jb::gated` with (gate_limit, gate_alpha): limit <= 0 is SiLU.
+// Mode SWIGLU applies `jb::gated` with (gate_limit, gate_alpha): limit 0 is SiLU, limit < 0 the tanh form of GELU.
 // Meant for prompt-sized T.  status codes of a timed-out wait: 21 producer, 22 MMA, 23 epilogue.
 JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
                                 int N_out, int K, int ldy, int mode, int split_k, int whole_tiles, float gate_limit,

@@ -1,0 +1,348 @@
+// The selective state-space mixer (Mamba-2 form: one scalar decay per head and token), as a recurrence over
+// the tokens of each sequence, with the short causal convolution in front of it and the gated, grouped norm
+// behind it.  Everything here is float32.
+//
+//   u = the projection's columns [x | B | C]            (x: [heads][P], B and C: [groups][N])
+//   xbc_t = silu(bias + sum_j w[:, j] u_(t - taps + 1 + j))   (zeros before a sequence's start; the last taps - 1
+//                                                              inputs of a sequence are kept as state)
+//   dt_t = softplus(dt_raw_t + dt_bias_h),  a_t = exp(-exp(A_log_h) dt_t)
+//   per head h (group g = h / (heads / groups)):
+//       S_t = a_t S_(t-1) + dt_t B_t x_t^T               (S: [N, P] float32, kept per sequence)
+//       y_t = S_t^T C_t + D_h x_t
+//   out = (y * silu(z)) / rms over each of `parts` equal pieces * w
+//
+// mamba2_scan: a block owns one (sequence, head, block of EB value columns); a thread owns two value columns and a
+// quarter of the rows of S in registers, walks the tokens in order (chunks of CT tokens are staged in shared memory,
+// dt and a computed on the way), and the four partial sums of y meet by shuffles in a fixed order.  The state is read
+// from and written back to the sequence's slot, so prompts, portions of prompts and single tokens are the same code.
+//
+// Long prompts run in segments of `seg_len` tokens so that the segments of one sequence run side by side: (1) every
+// segment but a sequence's last computes the state it would reach from zero and the product of its decays, (2) a
+// prefix pass turns these into every segment's starting state, start_(s+1) = decay_s start_s + local_s, (3) every
+// segment walks its tokens again from its starting state and writes the outputs; the last one leaves the
+// sequence's state.
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int PARTS = 4;      // threads that share a value column (each a quarter of the rows)
+constexpr int EB = 64;        // value columns a block owns, two a thread
+constexpr int CT = 16;        // tokens staged at a time
+constexpr int THREADS = EB / 2 * PARTS;
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+// log(1 + exp(z)); beyond 20 the sum is z itself in float32
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// ---- the short convolution ------------------------------------------------------------------------------
+// proj rows of ld floats, the convolved channels in columns [col0, col0 + C); w [C][taps], bias [C] (may be null);
+// state: per slot `slot_stride` floats, the convolution's part at `state_off`: [taps - 1][C], the inputs just before
+// the tokens of this step; out [T, C].
+__global__ void causal_conv_silu_kernel(const float* __restrict__ proj, int ld, int col0, int C,
+                                        const float* __restrict__ w, const float* __restrict__ bias, int taps,
+                                        const float* __restrict__ state, long long slot_stride, long long state_off,
+                                        const int* __restrict__ token_seq, const int* __restrict__ q_start,
+                                        const int* __restrict__ seq_slot, float* __restrict__ out) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = token_seq[t];
+  const int s0 = q_start[seq], li = t - s0;
+  const float* st = state + (size_t)seq_slot[seq] * slot_stride + state_off;
+  float acc = bias != nullptr ? bias[c] : 0.0f;
+  for (int j = 0; j < taps; ++j) {
+    const int src = li - (taps - 1) + j;
+    const float u = src >= 0 ? proj[(size_t)(s0 + src) * ld + col0 + c] : st[(size_t)(taps - 1 + src) * C + c];
+    acc = fmaf(w[(size_t)c * taps + j], u, acc);
+  }
+  out[(size_t)t * C + c] = silu_f(acc);
+}
+
+// After a step: the state becomes the last taps - 1 inputs of each sequence (older ones move up when the step
+// brought fewer tokens than that).  One thread per (sequence, channel) walks the rows in order, so a row is read
+// before it is written.
+__global__ void conv_state_shift_kernel(const float* __restrict__ proj, int ld, int col0, int C, int taps,
+                                        float* __restrict__ state, long long slot_stride, long long state_off,
+                                        const int* __restrict__ q_start, const int* __restrict__ seq_slot) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int seq = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s0 = q_start[seq], n = q_start[seq + 1] - s0;
+  float* st = state + (size_t)seq_slot[seq] * slot_stride + state_off;
+  for (int s = 0; s < taps - 1; ++s) {
+    const int src = n - (taps - 1) + s;              // index among this step's tokens
+    st[(size_t)s * C + c] = src >= 0 ? proj[(size_t)(s0 + src) * ld + col0 + c] : st[(size_t)(s + n) * C + c];
+  }
+}
+
+// ---- the recurrence -----------------------------------------------------------------------------------------
+enum { WHOLE = 0, LOCAL = 1, FROM_START = 3 };
+
+// RMAX: rows of S a thread holds (a multiple of 4, 4 RMAX >= N); shared rows are padded to 4 RMAX with zeros
+template <int RMAX, int PHASE>
+__global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kernel(
+    const float* __restrict__ xbc, int ldx, int b_col, int c_col, const float* __restrict__ dt_raw, int ld_dt,
+    const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+    float* __restrict__ out, float* __restrict__ state, long long slot_stride, long long state_off,
+    const int* __restrict__ q_start, const int* __restrict__ seq_slot, int H, int G, int N, int P, int seg_len,
+    int tiles_per_seq, float* __restrict__ scratch, float* __restrict__ seg_decay) {
+  constexpr int phase = PHASE;
+  constexpr int DP = PARTS * RMAX;         // padded rows
+  extern __shared__ __align__(16) float smem[];          // B [CT][DP], C [CT][DP], x [CT][EB], dt [CT], a [CT]
+  float* b_s = smem;
+  float* c_s = b_s + CT * DP;
+  float* x_s = c_s + CT * DP;
+  float* dt_s = x_s + CT * EB;
+  float* a_s = dt_s + CT;
+  jb::pdl_launch_dependents();
+  const int seq = blockIdx.x / tiles_per_seq, seg = blockIdx.x % tiles_per_seq;
+  const int h = blockIdx.y, e0 = blockIdx.z * EB;
+  const int g = h / (H / G);
+  const int part = threadIdx.x % PARTS, col = threadIdx.x / PARTS;
+  const int j0 = e0 + 2 * col, j1 = j0 + 1;
+  const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
+  jb::pdl_wait();
+  const int s0 = q_start[seq], q_len = q_start[seq + 1] - s0;
+  if ((long long)seg * seg_len >= q_len) return;
+  const int t0 = s0 + seg * seg_len, t1 = min(s0 + q_len, t0 + seg_len);
+  const bool last = t1 == s0 + q_len;
+  if (phase == LOCAL && last) return;              // nobody needs the last segment's state from zero
+  const size_t per_head = (size_t)N * P;
+  float* st = state + (size_t)seq_slot[seq] * slot_stride + state_off + (size_t)h * per_head;     // [N][P]
+  float* sc = scratch ? scratch + ((size_t)blockIdx.x * H + h) * per_head : nullptr;
+  const float* init = phase == WHOLE ? st : phase == FROM_START ? sc : nullptr;
+  float S0[RMAX], S1[RMAX];
+#pragma unroll
+  for (int i = 0; i < RMAX; ++i) {
+    const int r = part * RMAX + i;
+    S0[i] = (init && r < N && j0 < P) ? init[(size_t)r * P + j0] : 0.0f;
+    S1[i] = (init && r < N && j1 < P) ? init[(size_t)r * P + j1] : 0.0f;
+  }
+  float decay_all = 1.0f;
+  for (int c0 = t0; c0 < t1; c0 += CT) {
+    const int n = min(CT, t1 - c0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * DP; idx += THREADS) {
+      const int tt = idx / DP, r = idx % DP;
+      const bool in = r < N;
+      const float* row = xbc + (size_t)(c0 + tt) * ldx + (size_t)g * N + (in ? r : 0);
+      b_s[idx] = in ? row[b_col] : 0.0f;
+      if (phase != LOCAL) c_s[idx] = in ? row[c_col] : 0.0f;
+    }
+    for (int idx = threadIdx.x; idx < CT * EB; idx += THREADS) {
+      const int tt = idx / EB, c = idx % EB;
+      x_s[idx] = (tt < n && e0 + c < P) ? xbc[(size_t)(c0 + tt) * ldx + (size_t)h * P + e0 + c] : 0.0f;
+    }
+    if (threadIdx.x < n) {
+      const float dt = softplus_f(dt_raw[(size_t)(c0 + threadIdx.x) * ld_dt + h] + bias);
+      dt_s[threadIdx.x] = dt;
+      a_s[threadIdx.x] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < n; ++tt) {
+      const float a = a_s[tt], dt = dt_s[tt];
+      const float2 x = *reinterpret_cast<const float2*>(x_s + tt * EB + 2 * col);
+      const float v0 = dt * x.x, v1 = dt * x.y;
+      const float4* cr = reinterpret_cast<const float4*>(c_s + tt * DP + part * RMAX);
+      const float4* br = reinterpret_cast<const float4*>(b_s + tt * DP + part * RMAX);
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
+      if (phase == LOCAL) decay_all *= a;
+#pragma unroll
+      for (int i = 0; i < RMAX / 4; ++i) {
+        const float4 k4 = br[i];
+        S0[4 * i] = fmaf(a, S0[4 * i], k4.x * v0);
+        S0[4 * i + 1] = fmaf(a, S0[4 * i + 1], k4.y * v0);
+        S0[4 * i + 2] = fmaf(a, S0[4 * i + 2], k4.z * v0);
+        S0[4 * i + 3] = fmaf(a, S0[4 * i + 3], k4.w * v0);
+        S1[4 * i] = fmaf(a, S1[4 * i], k4.x * v1);
+        S1[4 * i + 1] = fmaf(a, S1[4 * i + 1], k4.y * v1);
+        S1[4 * i + 2] = fmaf(a, S1[4 * i + 2], k4.z * v1);
+        S1[4 * i + 3] = fmaf(a, S1[4 * i + 3], k4.w * v1);
+        if (phase != LOCAL) {
+          const float4 q4 = cr[i];
+          a0 = fmaf(S0[4 * i], q4.x, a0);
+          a1 = fmaf(S0[4 * i + 1], q4.y, a1);
+          a2 = fmaf(S0[4 * i + 2], q4.z, a2);
+          a3 = fmaf(S0[4 * i + 3], q4.w, a3);
+          b0 = fmaf(S1[4 * i], q4.x, b0);
+          b1 = fmaf(S1[4 * i + 1], q4.y, b1);
+          b2 = fmaf(S1[4 * i + 2], q4.z, b2);
+          b3 = fmaf(S1[4 * i + 3], q4.w, b3);
+        }
+      }
+      if (phase != LOCAL) {
+        float acc0 = (a0 + a1) + (a2 + a3), acc1 = (b0 + b1) + (b2 + b3);
+        // the four parts of a column are neighbouring lanes: part 0 + 1, 2 + 3, then the two sums
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        if (part == 0) {
+          float* orow = out + (size_t)(c0 + tt) * H * P + (size_t)h * P;
+          if (j0 < P) orow[j0] = fmaf(dskip, x.x, acc0);
+          if (j1 < P) orow[j1] = fmaf(dskip, x.y, acc1);
+        }
+      }
+    }
+  }
+  if (phase == LOCAL && blockIdx.z == 0 && threadIdx.x == 0) seg_decay[(size_t)blockIdx.x * H + h] = decay_all;
+  float* dst = phase == LOCAL ? sc : (last ? st : nullptr);
+  if (dst == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < RMAX; ++i) {
+    const int r = part * RMAX + i;
+    if (r < N && j0 < P) dst[(size_t)r * P + j0] = S0[i];
+    if (r < N && j1 < P) dst[(size_t)r * P + j1] = S1[i];
+  }
+}
+
+// scratch[seq][seg] holds segment seg's state from zero; afterwards it holds the state the segment starts from
+__global__ void mamba2_prefix_kernel(float* __restrict__ scratch, const float* __restrict__ seg_decay,
+                                     const float* __restrict__ state, long long slot_stride, long long state_off,
+                                     const int* __restrict__ q_start, const int* __restrict__ seq_slot, int H, int N,
+                                     int P, int seg_len, int tiles_per_seq) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int seq = blockIdx.x;
+  const size_t per = (size_t)H * N * P;
+  const size_t idx = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+  if (idx >= per) return;
+  const int h = (int)(idx / ((size_t)N * P));
+  const int q_len = q_start[seq + 1] - q_start[seq];
+  const int n_seg = (q_len + seg_len - 1) / seg_len;
+  float S = state[(size_t)seq_slot[seq] * slot_stride + state_off + idx];
+  float* p = scratch + (size_t)seq * tiles_per_seq * per + idx;
+  const float* dec = seg_decay + (size_t)seq * tiles_per_seq * H + h;
+  for (int seg = 0; seg < n_seg; ++seg) {
+    const bool has_local = seg + 1 < n_seg;          // the last segment left nothing
+    const float local = has_local ? p[(size_t)seg * per] : 0.0f;
+    const float d = has_local ? dec[(size_t)seg * H] : 0.0f;
+    p[(size_t)seg * per] = S;
+    S = fmaf(d, S, local);
+  }
+}
+
+// ---- gate, then a norm over each of `parts` equal pieces ------------------------------------------------------
+template <typename TO>
+__global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int gate_ld,
+                                           const float* __restrict__ w, float eps, TO* __restrict__ out, int N,
+                                           int parts) {
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x, piece = blockIdx.y;
+  const int n = N / parts, c0 = piece * n;
+  const float* row = y + (size_t)t * N + c0;
+  const float* g = gate + (size_t)t * gate_ld + c0;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = row[i] * silu_f(g[i]);
+    ss += v * v;
+  }
+  ss = jb::block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    out[(size_t)t * N + c0 + i] = jb::from_f32<TO>(((row[i] * silu_f(g[i])) / rms) * w[c0 + i]);
+}
+
+}  // namespace
+
+// out[t, c] = silu(bias[c] + sum_j w[c][j] u[t - taps + 1 + j][c]) over the columns [col0, col0 + C) of proj.
+// update_state != 0: afterwards the state takes the last taps - 1 inputs of every sequence (a second launch).
+JB_EXPORT int jb_causal_conv_silu(const float* proj, int ld, int col0, int C, const float* w, const float* bias, int taps,
+                                  float* state, long long slot_stride, long long state_off, const int* token_seq,
+                                  const int* q_start, const int* seq_slot, float* out, int T, int n_seqs,
+                                  int update_state, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(taps < 1 || ld < col0 + C, "causal_conv_silu: %d taps over columns %d..%d of %d", taps, col0, col0 + C, ld);
+  JB_REFUSE(taps > 1 && state == nullptr, "causal_conv_silu: a convolution of %d taps needs its state", taps);
+  {
+    jb::Launch cfg(dim3(T, (C + 127) / 128), dim3(128), 0, stream);
+    cudaError_t e = cudaLaunchKernelEx(&cfg.c, causal_conv_silu_kernel, proj, ld, col0, C, w, bias, taps,
+                                       (const float*)state, slot_stride, state_off, token_seq, q_start, seq_slot, out);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (update_state && taps > 1) {
+    jb::Launch cfg(dim3(n_seqs, (C + 127) / 128), dim3(128), 0, stream);
+    cudaError_t e = cudaLaunchKernelEx(&cfg.c, conv_state_shift_kernel, proj, ld, col0, C, taps, state, slot_stride,
+                                       state_off, q_start, seq_slot);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+// xbc: float32 [T, ldx], x in columns [0, H P), B at b_col ([G][N]), C at c_col ([G][N]); dt_raw: float32 rows of
+// ld_dt floats, head h in column h; dt_bias, A_log, Dskip: [H] float32; out: float32 [T, H P]; state: per slot
+// slot_stride floats, the recurrence's [H][N][P] at state_off.  seg_len > 0 with scratch (n_seqs *
+// ceil(max_q_len / seg_len) * H * N * P floats) and seg_decay (n_seqs * ceil(max_q_len / seg_len) * H floats)
+// runs the three passes over segments; seg_len = 0 walks every sequence in one block per column block.
+JB_EXPORT int jb_mamba2_scan(const float* xbc, int ldx, int b_col, int c_col, const float* dt_raw, int ld_dt,
+                             const float* dt_bias, const float* A_log, const float* Dskip, float* out, float* state,
+                             long long slot_stride, long long state_off, const int* q_start, const int* seq_slot,
+                             int n_seqs, int H, int G, int N, int P, int max_q_len, int seg_len, float* scratch,
+                             float* seg_decay, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  JB_REFUSE(N < 1 || N > 256 || P < 1, "mamba2_scan: state size %d is outside [1, 256]", N);
+  JB_REFUSE(G < 1 || H % G != 0, "mamba2_scan: %d heads are not a multiple of %d groups", H, G);
+  JB_REFUSE(seg_len > 0 && (scratch == nullptr || seg_decay == nullptr), "mamba2_scan: segments need scratch");
+  const int rmax = N <= 64 ? 16 : N <= 128 ? 32 : 64;
+  const size_t smem = (size_t)(2 * CT * PARTS * rmax + CT * EB + 2 * CT) * sizeof(float);
+  const bool segmented = seg_len > 0;
+  const int tiles = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
+  const int seg = segmented ? seg_len : 0x40000000;
+#define JB_LAUNCH_MS(RM, PHASE)                                                                                      \
+  do {                                                                                                               \
+    jb::Launch cfg(dim3(n_seqs * tiles, H, (P + EB - 1) / EB), dim3(THREADS), smem, stream);                         \
+    cudaError_t err = cudaLaunchKernelEx(&cfg.c, mamba2_scan_kernel<RM, PHASE>, xbc, ldx, b_col, c_col, dt_raw,     \
+                                         ld_dt, dt_bias, A_log, Dskip, out, state, slot_stride, state_off, q_start, \
+                                         seq_slot, H, G, N, P, seg, tiles, scratch, seg_decay);                      \
+    if (err != cudaSuccess) return (int)err;                                                                         \
+  } while (0)
+#define JB_LAUNCH_MS_R(PHASE)                       \
+  do {                                              \
+    if (rmax == 16) JB_LAUNCH_MS(16, PHASE);        \
+    else if (rmax == 32) JB_LAUNCH_MS(32, PHASE);   \
+    else JB_LAUNCH_MS(64, PHASE);                   \
+  } while (0)
+  if (!segmented) {
+    JB_LAUNCH_MS_R(WHOLE);
+    return 0;
+  }
+  JB_LAUNCH_MS_R(LOCAL);
+  {
+    const size_t per = (size_t)H * N * P;
+    jb::Launch cfg(dim3(n_seqs, (unsigned)((per + 255) / 256)), dim3(256), 0, stream);
+    cudaError_t err = cudaLaunchKernelEx(&cfg.c, mamba2_prefix_kernel, scratch, (const float*)seg_decay,
+                                         (const float*)state, slot_stride, state_off, q_start, seq_slot, H, N, P,
+                                         seg_len, tiles);
+    if (err != cudaSuccess) return (int)err;
+  }
+  JB_LAUNCH_MS_R(FROM_START);
+#undef JB_LAUNCH_MS_R
+#undef JB_LAUNCH_MS
+  return 0;
+}
+
+// out[t] = (y[t] * silu(gate[t])) divided, in each of `parts` equal pieces, by the piece's root mean square, times w.
+// y: float32 [T, N]; gate: float32 rows of gate_ld; w: [N] float32; out [T, N] in out_dtype.
+JB_EXPORT int jb_gated_group_rmsnorm(const float* y, const float* gate, int gate_ld, const float* w, float eps,
+                                     void* out, int out_dtype, int T, int N, int parts, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(parts < 1 || N % parts != 0, "gated_group_rmsnorm: %d numbers do not fall into %d equal pieces", N, parts);
+  jb::Launch cfg(dim3(T, parts), dim3(N / parts >= 2048 ? 256 : 128), 0, stream);
+  if (out_dtype == JB_F32)
+    return (int)cudaLaunchKernelEx(&cfg.c, gated_group_rmsnorm_kernel<float>, y, gate, gate_ld, w, eps, (float*)out, N,
+                                   parts);
+  if (out_dtype == JB_BF16)
+    return (int)cudaLaunchKernelEx(&cfg.c, gated_group_rmsnorm_kernel<bf16>, y, gate, gate_ld, w, eps, (bf16*)out, N,
+                                   parts);
+  return JB_ERR_BAD_DTYPE;
+}

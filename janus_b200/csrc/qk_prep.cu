@@ -1,0 +1,160 @@
+// What happens between the projections of an attention mixer and the attention kernel itself, for two mixers
+// whose queries and keys are normed over the whole projection.  All arithmetic is float32; the projections are the
+// products' float32 accumulators.
+//
+// qk_norm_rope_cache (attention whose values are its keys as projected):
+//   q = proj[:, 0 : H d] + bq,  k = proj[:, H d : (H + G) d] + bk
+//   v = k                                             (before norm and rotation; appended to the value pages)
+//   q <- q / sqrt(mean(q^2) + eps) * wq               (one root mean square over all H d numbers), k likewise
+//   the first `rot` dimensions of every head of q and k are turned in the pairing (i, i + rot/2) by the angle
+//   of the token's position (cos and sin from a table [positions][rot/2][2]); the rest pass
+//   q is written [T, H d] in the engine dtype, k is appended to the key pages.
+//
+// latent_prep (latent attention, queries already multiplied into the latent space):
+//   q = proj[:, 0 : Q] written [T, Q] in the engine dtype
+//   c = proj[:, Q : Q + r] / sqrt(mean(.^2) + eps) * w, appended to the pages as the token's one key row
+//
+// Pages of one place: [page][kv_head][page_size][size]; dest[t] = page * page_size + row of token t.
+// One block per token.
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename TO>
+__global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bq,
+                                          const float* __restrict__ bk, const float* __restrict__ wq,
+                                          const float* __restrict__ wk, float eps, const float* __restrict__ table,
+                                          int rot, const int* __restrict__ positions, TO* __restrict__ q_out,
+                                          const int* __restrict__ dest, TO* __restrict__ k_cache,
+                                          TO* __restrict__ v_cache, int H, int G, int d, int page_size, int write_kv) {
+  extern __shared__ __align__(16) float row_s[];     // q [H d], then k [G d]
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  const int QW = H * d, KW = write_kv ? G * d : 0;
+  const float* pr = proj + (size_t)t * ld;
+  size_t page = 0;
+  int prow = 0;
+  if (write_kv) {
+    page = (size_t)(dest[t] / page_size);
+    prow = dest[t] % page_size;
+  }
+  float sq = 0.0f, sk = 0.0f;
+  for (int i = threadIdx.x; i < QW + KW; i += blockDim.x) {
+    float v = pr[i];
+    if (i < QW) {
+      if (bq != nullptr) v += bq[i];
+      sq += v * v;
+    } else {
+      const int c = i - QW;
+      if (bk != nullptr) v += bk[c];
+      sk += v * v;
+      const int g = c / d, j = c % d;
+      v_cache[((page * G + g) * page_size + prow) * d + j] = jb::from_f32<TO>(v);
+    }
+    row_s[i] = v;
+  }
+  sq = jb::block_sum(sq, scratch);
+  const float rq = sqrtf(sq / (float)QW + eps);
+  float rk = 1.0f;
+  if (write_kv) {
+    sk = jb::block_sum(sk, scratch);
+    rk = sqrtf(sk / (float)KW + eps);
+  }
+  const int half = rot >> 1;
+  const float* cs = (table != nullptr && rot > 0) ? table + (size_t)positions[t] * half * 2 : nullptr;
+  // a thread takes a number and, where it is rotated, writes both members of its pair
+  for (int i = threadIdx.x; i < QW + KW; i += blockDim.x) {
+    const bool is_q = i < QW;
+    const int c = is_q ? i : i - QW;
+    const int head = c / d, j = c % d;
+    const float* w = is_q ? wq : wk;
+    const float r = is_q ? rq : rk;
+    TO* out = is_q ? q_out + (size_t)t * QW + (size_t)head * d
+                   : k_cache + ((page * G + head) * page_size + prow) * d;
+    if (cs != nullptr && j < rot) {
+      if (j >= half) continue;                       // written by the thread of the pair's first member
+      const float u = (row_s[i] / r) * w[c], v = (row_s[i + half] / r) * w[c + half];
+      const float co = cs[2 * j], si = cs[2 * j + 1];
+      out[j] = jb::from_f32<TO>(u * co - v * si);
+      out[j + half] = jb::from_f32<TO>(v * co + u * si);
+    } else {
+      out[j] = jb::from_f32<TO>((row_s[i] / r) * w[c]);
+    }
+  }
+}
+
+template <typename TO>
+__global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int Q, int r, const float* __restrict__ w,
+                                   float eps, TO* __restrict__ q_out, const int* __restrict__ dest,
+                                   TO* __restrict__ c_cache, int write_c) {
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  const float* pr = proj + (size_t)t * ld;
+  for (int i = threadIdx.x; i < Q; i += blockDim.x) q_out[(size_t)t * Q + i] = jb::from_f32<TO>(pr[i]);
+  if (!write_c) return;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < r; i += blockDim.x) ss += pr[Q + i] * pr[Q + i];
+  ss = jb::block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)r + eps);
+  TO* out = c_cache + (size_t)dest[t] * r;          // one key head: row dest[t] of [page * page_size][r]
+  for (int i = threadIdx.x; i < r; i += blockDim.x) out[i] = jb::from_f32<TO>((pr[Q + i] / rms) * w[i]);
+}
+
+}  // namespace
+
+// proj: float32 [T, ld]; bq [H d], bk [G d] (either may be null), wq [H d], wk [G d] float32; table: float32
+// [positions][rot/2][2] or null (no rotation); q_out [T, H d] and the pages in out_dtype.  write_kv = 0: q only
+// (a place that reads the keys and values another place wrote).
+JB_EXPORT int jb_qk_norm_rope_cache(const float* proj, int ld, const float* bq, const float* bk, const float* wq,
+                                    const float* wk, float eps, const float* table, int rot, const int* positions,
+                                    void* q_out, int out_dtype, const int* dest, void* k_cache, void* v_cache, int T,
+                                    int H, int G, int d, int page_size, int write_kv, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(rot < 0 || rot > d || (rot & 1), "qk_norm_rope_cache: %d rotated dimensions do not fit a head of %d", rot, d);
+  JB_REFUSE(ld < (H + (write_kv ? G : 0)) * d, "qk_norm_rope_cache: rows of %d floats do not hold the projections", ld);
+  const size_t smem = (size_t)(H + (write_kv ? G : 0)) * d * sizeof(float);
+  JB_REFUSE(smem > 200 * 1024, "qk_norm_rope_cache: a token's projections (%zu bytes) do not fit shared memory", smem);
+  jb::Launch cfg(dim3(T), dim3(256), smem, stream);
+  cudaError_t e;
+#define JB_LAUNCH_QK(TO)                                                                                               \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024) {                                                                                            \
+      e = cudaFuncSetAttribute(qk_norm_rope_cache_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                             \
+    }                                                                                                                  \
+    e = cudaLaunchKernelEx(&cfg.c, qk_norm_rope_cache_kernel<TO>, proj, ld, bq, bk, wq, wk, eps, table, rot,           \
+                           positions, (TO*)q_out, dest, (TO*)k_cache, (TO*)v_cache, H, G, d, page_size, write_kv);    \
+  } while (0)
+  if (out_dtype == JB_F32) JB_LAUNCH_QK(float);
+  else if (out_dtype == JB_BF16) JB_LAUNCH_QK(bf16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_QK
+  return (int)e;
+}
+
+// proj: float32 [T, ld] with the queries in columns [0, Q) and the latent projection in [Q, Q + r); w [r] float32;
+// q_out [T, Q] and the pages ([page][1][page_size][r]) in out_dtype.  write_c = 0: queries only.
+JB_EXPORT int jb_latent_prep(const float* proj, int ld, int Q, int r, const float* w, float eps, void* q_out,
+                             int out_dtype, const int* dest, void* c_cache, int T, int write_c, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(ld < Q + (write_c ? r : 0), "latent_prep: rows of %d floats do not hold the projections", ld);
+  jb::Launch cfg(dim3(T), dim3(256), 0, stream);
+  cudaError_t e;
+  if (out_dtype == JB_F32)
+    e = cudaLaunchKernelEx(&cfg.c, latent_prep_kernel<float>, proj, ld, Q, r, w, eps, (float*)q_out, dest,
+                           (float*)c_cache, write_c);
+  else if (out_dtype == JB_BF16)
+    e = cudaLaunchKernelEx(&cfg.c, latent_prep_kernel<bf16>, proj, ld, Q, r, w, eps, (bf16*)q_out, dest,
+                           (bf16*)c_cache, write_c);
+  else
+    return JB_ERR_BAD_DTYPE;
+  return (int)e;
+}

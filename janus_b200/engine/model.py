@@ -34,7 +34,7 @@ class DecoderModel:
         for ls in spec.layers:
             objs = {attr: make_part(family, ps, dtype, device) for attr, family, ps in _layer_parts(ls)}
             self._layer_part_objs.append(objs)
-            self.layers.append(_arrange(ls.arrangement, objs, spec.hidden_size, dtype))
+            self.layers.append(_arrange(ls.arrangement, objs, spec.hidden_size, dtype, dict(ls.arrangement_params)))
         self.final_norm = make_part("norm", spec.final_norm, dtype, device)
         self.embedding_transforms = [make_part("transform", ps, dtype, device) for ps in spec.embedding_transforms]
         self.logit_transforms = [make_part("transform", ps, dtype, device) for ps in spec.logit_transforms]
@@ -129,13 +129,13 @@ class DecoderModel:
             transform.forward(logits, ctx)
 
 
-def _arrange(kind: str, objs: Dict[str, object], hidden_size: int, dtype: torch.dtype):
+def _arrange(kind: str, objs: Dict[str, object], hidden_size: int, dtype: torch.dtype, params: Optional[dict] = None):
     from ..parts.base import _REGISTRIES
     try:
         factory = _REGISTRIES["arrangement"][kind]
     except KeyError:
         raise KeyError(f"no arrangement '{kind}' is registered") from None
-    return factory(objs, hidden_size, dtype)
+    return factory(objs, hidden_size, dtype, **(params or {}))
 
 
 def model_weight_specs(spec: ModelSpec, layer_part_objs=None, final_norm=None, transforms=None) -> List[TensorSpec]:

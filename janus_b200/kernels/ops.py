@@ -68,7 +68,10 @@ _SIGNATURES = {
     "jb_conv_rope_cache": "pipipipppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
     "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
-    "jb_clamped_glu": "piipiiiffp", "jb_pad_rows_bf16": "pipiip", "jb_scale_softcap": "plffp",
+    "jb_clamped_glu": "piipiiiffp",
+    "jb_sublayer_norm_add": "ppiffppiiiplp", "jb_qk_norm_rope_cache": "pippppfpippipppiiiiiip",
+    "jb_latent_prep": "piiipfpippiip", "jb_causal_conv_silu": "piiippipllppppiiip",
+    "jb_mamba2_scan": "piiipipppppllppiiiiiiippp", "jb_gated_group_rmsnorm": "ppipfpiiiip", "jb_pad_rows_bf16": "pipiip", "jb_scale_softcap": "plffp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
            "f": ctypes.c_float}
@@ -1116,8 +1119,12 @@ def diff_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 
 
 # -- a gated activation with clamped branches; scale and soft cap -------------------------------
+GELU_TANH_GATE = -1.0     # as a gated product's `limit`: the tanh form of GELU on the gate (any negative value)
+
+
 def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, up_col: int, limit: float, alpha: float) -> None:
-    """out[t, c] = g sigmoid(alpha g) (u + 1), g = min(gate_up[t, c], limit), u = clamp(gate_up[t, up_col + c], +-limit)."""
+    """out[t, c] = g sigmoid(alpha g) (u + 1), g = min(gate_up[t, c], limit), u = clamp(gate_up[t, up_col + c], +-limit);
+    with limit < 0 (`GELU_TANH_GATE`) out[t, c] = gelu_tanh(gate) * up, with limit 0 silu(gate) * up."""
     T, I = out.shape
     _need(gate_up, "gate/up", torch.float32)
     _need(out, "activation out")
@@ -1141,3 +1148,167 @@ def pad_rows_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
     if out.shape[0] != T or out.shape[1] < K:
         raise KernelError(f"pad_rows: {tuple(out.shape)} does not hold {tuple(x.shape)}")
     _check(_lib("elementwise").jb_pad_rows_bf16(_ptr(x), K, _ptr(out), out.shape[1], T, _stream()), "pad_rows")
+
+
+# -- a sublayer whose output is normed before it joins the residual stream ---------------------------------
+def sublayer_norm_add(y: Optional[torch.Tensor], gamma: Optional[torch.Tensor], eps: float, mult: float,
+                      residual: torch.Tensor, x_out: Optional[torch.Tensor],
+                      clear: Optional[torch.Tensor] = None) -> None:
+    """residual += mult * y / sqrt(mean(y^2) + eps) * gamma (row by row; y float32, set to zero afterwards), then
+    x_out = residual in x_out's dtype.  y None: the cast alone; x_out None: the sum alone.  `clear`: a float32
+    scratch tensor (whole 16-byte vectors) that the same launch sets to zero."""
+    T, H = residual.shape
+    _need(residual, "residual", torch.float32)
+    if y is not None:
+        _need(y, "sublayer output", torch.float32, (T, H))
+        _need(gamma, "norm weight", None, (H,))
+    if x_out is not None:
+        _need(x_out, "sublayer input", None, (T, H))
+    if clear is not None:
+        _need(clear, "buffer to clear", torch.float32)
+    _check(_lib("elementwise").jb_sublayer_norm_add(
+        _ptr(y), _ptr(gamma) if y is not None else None, dtype_code(gamma.dtype) if y is not None else F32, eps, mult,
+        _ptr(residual), _ptr(x_out), dtype_code(x_out.dtype) if x_out is not None else F32, T, H, _ptr(clear),
+        0 if clear is None else clear.numel(), _stream()), "sublayer_norm_add")
+
+
+# -- attention mixers whose queries and keys are normed over the whole projection ----------------------------
+def qk_norm_rope_cache(proj: torch.Tensor, bq: Optional[torch.Tensor], bk: Optional[torch.Tensor], wq: torch.Tensor,
+                       wk: torch.Tensor, eps: float, table: Optional[torch.Tensor], rot: int, positions: torch.Tensor,
+                       q_out: torch.Tensor, dest: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                       v_cache: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, page_size: int,
+                       write_kv: bool = True) -> None:
+    """proj float32 [T, >= (heads + kv_heads) dim]: q and k as projected.  Adds the biases, appends k (with its bias,
+    before norm and rotation) to the value pages, norms q and k each over its whole row, turns the first `rot`
+    dimensions of every head by the table's cos and sin at the token's position, writes q [T, heads dim] and
+    appends k to the key pages.  write_kv False: q alone."""
+    T = q_out.shape[0]
+    _need(proj, "projections", torch.float32)
+    if proj.shape[0] != T:
+        raise KernelError("qk_norm_rope_cache: projections and queries differ in their rows")
+    _need(q_out, "q_out", None, (T, heads * dim))
+    _need(wq, "q norm weight", torch.float32, (heads * dim,))
+    _need(positions, "positions", torch.int32, (T,))
+    if bq is not None:
+        _need(bq, "q bias", torch.float32, (heads * dim,))
+    if table is not None and rot > 0:
+        _need(table, "rotation table", torch.float32)
+        if tuple(table.shape[1:]) != (rot // 2, 2):
+            raise KernelError(f"qk_norm_rope_cache: table of shape {tuple(table.shape)} does not fit {rot} dimensions")
+    if write_kv:
+        _need(wk, "k norm weight", torch.float32, (kv_heads * dim,))
+        if bk is not None:
+            _need(bk, "k bias", torch.float32, (kv_heads * dim,))
+        _need(dest, "cache rows", torch.int32, (T,))
+        _need(k_cache, "key pages", q_out.dtype)
+        _need(v_cache, "value pages", q_out.dtype)
+    _check(_lib("qk_prep").jb_qk_norm_rope_cache(
+        _ptr(proj), proj.shape[1], _ptr(bq), _ptr(bk) if write_kv else None, _ptr(wq), _ptr(wk) if write_kv else None,
+        eps, _ptr(table) if rot > 0 else None, int(rot), _ptr(positions), _ptr(q_out), dtype_code(q_out.dtype),
+        _ptr(dest) if write_kv else None, _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None,
+        T, heads, kv_heads, dim, page_size, int(write_kv), _stream()), "qk_norm_rope_cache")
+
+
+def latent_prep(proj: torch.Tensor, q_width: int, rank: int, weight: Optional[torch.Tensor], eps: float,
+                q_out: torch.Tensor, dest: Optional[torch.Tensor], c_cache: Optional[torch.Tensor],
+                write_c: bool = True) -> None:
+    """proj float32 [T, >= q_width (+ rank)]: q_out = the first q_width columns in q_out's dtype; the next `rank`
+    columns, divided by their root mean square and multiplied by `weight`, are appended to the pages as the token's
+    key row (one key head of size rank).  write_c False: the queries alone."""
+    T = q_out.shape[0]
+    _need(proj, "projections", torch.float32)
+    if proj.shape[0] != T:
+        raise KernelError("latent_prep: projections and queries differ in their rows")
+    _need(q_out, "q_out", None, (T, q_width))
+    if write_c:
+        _need(weight, "latent norm weight", torch.float32, (rank,))
+        _need(dest, "cache rows", torch.int32, (T,))
+        _need(c_cache, "latent pages", q_out.dtype)
+    _check(_lib("qk_prep").jb_latent_prep(
+        _ptr(proj), proj.shape[1], int(q_width), int(rank), _ptr(weight) if write_c else None, eps, _ptr(q_out),
+        dtype_code(q_out.dtype), _ptr(dest) if write_c else None, _ptr(c_cache) if write_c else None, T, int(write_c),
+        _stream()), "latent_prep")
+
+
+# -- the selective state-space mixer ---------------------------------------------------------------------------
+MAMBA2_SEGMENT = 128     # tokens of a segment when a long prompt's recurrence runs in segments side by side
+
+
+def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                     taps: int, state: Optional[torch.Tensor], state_off: int, token_seq: torch.Tensor,
+                     q_start: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, n_seqs: int,
+                     update_state: bool = True) -> None:
+    """out[t, c] = silu(bias[c] + sum_j weight[c, j] u[t - taps + 1 + j, c]) with u the columns [col0, col0 + channels)
+    of proj (float32) within each sequence; the inputs before a step's first token come from `state` (float32
+    [slots, n], the convolution's [taps - 1, channels] block at offset state_off of a slot's row), which afterwards
+    takes the sequence's last taps - 1 inputs (a second launch)."""
+    T = proj.shape[0]
+    _need(proj, "projections", torch.float32)
+    _need(out, "convolution out", torch.float32, (T, channels))
+    _need(weight, "convolution weight", torch.float32, (channels, taps))
+    if bias is not None:
+        _need(bias, "convolution bias", torch.float32, (channels,))
+    if taps > 1:
+        _need(state, "convolution state", torch.float32)
+        if state.dim() != 2 or state_off + (taps - 1) * channels > state.shape[1]:
+            raise KernelError("causal_conv_silu: the state rows do not hold the convolution's inputs")
+    _need(token_seq, "token sequences", torch.int32, (T,))
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
+    two = bool(update_state and taps > 1)
+    _check(_lib("mamba2").jb_causal_conv_silu(
+        _ptr(proj), proj.shape[1], int(col0), int(channels), _ptr(weight), _ptr(bias), int(taps), _ptr(state),
+        state.shape[1] if state is not None else 0, int(state_off), _ptr(token_seq), _ptr(q_start), _ptr(seq_slot),
+        _ptr(out), T, n_seqs, int(two), _stream()), "causal_conv_silu", kernels=2 if two else 1)
+
+
+def mamba2_scan(xbc: torch.Tensor, b_col: int, c_col: int, dt_raw: torch.Tensor, dt_bias: torch.Tensor,
+                a_log: torch.Tensor, d_skip: torch.Tensor, out: torch.Tensor, state: torch.Tensor, state_off: int,
+                q_start: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int, heads: int, groups: int, n_state: int,
+                vdim: int, max_q_len: int = 1, workspace=None) -> None:
+    """Per sequence and head S <- a_t S + dt_t B_t x_t^T, out_t = S^T C_t + D x_t over the step's tokens in order, with
+    dt_t = softplus(dt_raw_t + dt_bias) and a_t = exp(-exp(a_log) dt_t).  xbc float32 [T, ld]: x in columns
+    [0, heads vdim), B at b_col and C at c_col ([groups][n_state]); dt_raw a float32 view [T, heads] of wider rows;
+    state float32 [slots, n] with the recurrence's [heads, n_state, vdim] block at offset state_off of a slot's row.
+    With a workspace, steps whose longest sequence brings more than two segments of tokens run in three passes over
+    segments (3 launches), else one launch."""
+    T = xbc.shape[0]
+    _need(xbc, "convolved x, B, C", torch.float32)
+    _need(out, "scan out", torch.float32, (T, heads * vdim))
+    _need(state, "scan state", torch.float32)
+    if state.dim() != 2 or state_off + heads * n_state * vdim > state.shape[1]:
+        raise KernelError("mamba2_scan: the state rows do not hold [heads, state, vdim]")
+    if _checks[0] and (dt_raw.dtype != torch.float32 or tuple(dt_raw.shape) != (T, heads) or dt_raw.stride(1) != 1):
+        raise KernelError("mamba2_scan: dt must be float32 [T, heads] with unit column stride")
+    for name, t in (("dt_bias", dt_bias), ("A_log", a_log), ("D", d_skip)):
+        _need(t, name, torch.float32, (heads,))
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
+    if max(heads * vdim, b_col + groups * n_state, c_col + groups * n_state) > xbc.shape[1]:
+        raise KernelError("mamba2_scan: the columns reach past the rows")
+    seg, scratch, seg_decay = 0, None, None
+    if workspace is not None and max_q_len > 2 * MAMBA2_SEGMENT:
+        seg = MAMBA2_SEGMENT
+        tiles = (max_q_len + seg - 1) // seg
+        scratch = workspace.get("mamba2_segments", (n_seqs * tiles * heads * n_state * vdim,), torch.float32)
+        seg_decay = workspace.get("mamba2_segment_decay", (n_seqs * tiles * heads,), torch.float32)
+    _check(_lib("mamba2").jb_mamba2_scan(
+        _ptr(xbc), xbc.shape[1], int(b_col), int(c_col), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log),
+        _ptr(d_skip), _ptr(out), _ptr(state), state.shape[1], int(state_off), _ptr(q_start), _ptr(seq_slot), n_seqs,
+        heads, groups, n_state, vdim, int(max_q_len), seg, _ptr(scratch), _ptr(seg_decay), _stream()),
+        "mamba2_scan", kernels=3 if seg else 1)
+
+
+def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, parts: int,
+                        out: torch.Tensor) -> None:
+    """out = (y * silu(gate)) divided, within each of `parts` equal pieces of a row, by the piece's root mean square
+    (eps inside the root), times weight; y float32 [T, N], gate a float32 view [T, N] of rows that may be wider."""
+    T, N = y.shape
+    _need(y, "gated norm input", torch.float32)
+    _need(weight, "gated norm weight", torch.float32, (N,))
+    _need(out, "gated norm out", None, (T, N))
+    if _checks[0] and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, N) or gate.stride(1) != 1):
+        raise KernelError("gated_group_rmsnorm: the gate must be float32 [T, N] with unit column stride")
+    _check(_lib("mamba2").jb_gated_group_rmsnorm(
+        _ptr(y), _ptr(gate), gate.stride(0), _ptr(weight), eps, _ptr(out), dtype_code(out.dtype), T, N, int(parts),
+        _stream()), "gated_group_rmsnorm")

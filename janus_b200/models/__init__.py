@@ -1,1 +1,1 @@
-from . import llama, zivitar  # noqa: F401  (registers LlamaForCausalLM and Zivitar)
+from . import llama, ramolix, zivitar  # noqa: F401  (registers LlamaForCausalLM, Ramolix and Zivitar)

@@ -41,6 +41,26 @@ def _check_kernel_limits(num_heads: int, num_kv_heads: int, head_dim: int, dtype
                              f"{head_dim} (at most {ops.ATTENTION_BF16_MAX_GROUP}); such a model runs with dtype float32")
 
 
+def attend_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, ctx, group,
+                 num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
+    """Causal attention of the step's queries (engine dtype, already in their final form) over pages that already
+    hold the step's own keys and values, by the kernel that fits the step: the float32 engine's CUDA-core kernel,
+    the split-key kernel for one token per sequence, the tcgen05 kernel (or, for shapes it does not take, the
+    mma.sync one) for prompts.  For mixers that prepare q and the cache rows in a kernel of their own."""
+    if q.dtype == torch.float32:
+        ops.attention_f32(q, k_cache, v_cache, out, group.block_table, ctx.token_seq, ctx.positions, num_heads,
+                          num_kv_heads, head_dim, group.page_size, window, scale)
+    elif ctx.is_decode:
+        ops.attention_bf16_decode(q, k_cache, v_cache, out, group.block_table, ctx.kv_len, num_heads, num_kv_heads,
+                                  head_dim, group.page_size, window, scale, ctx.workspace, ctx.max_kv_len_bound)
+    elif ops.attention_tc_supported(num_heads, num_kv_heads, head_dim):
+        ops.attention_tc_prefill(q, k_cache, v_cache, out, group.block_table, ctx.q_start, ctx.kv_len, ctx.n_seqs,
+                                 ctx.max_q_len, num_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+    else:
+        ops.attention_bf16_prefill(q, k_cache, v_cache, out, group.block_table, ctx.q_start, ctx.kv_len, ctx.n_seqs,
+                                   ctx.max_q_len, num_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+
+
 class GQAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, window: int = 0,

@@ -46,13 +46,16 @@ class KVSpec:
     """Keys and values per token.  window = 0 keeps every key; window = w keeps
     the last w keys (the query's own position included), and besides them the
     first `keep_first` keys of the sequence.  Values may differ from keys in
-    their number of heads and their size (0: as the keys)."""
+    their number of heads and their size (0: as the keys).  `values_are_keys`:
+    the place stores one row per token that serves as key and as value (a
+    latent vector that both are made from): no pages of their own for values."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     keep_first: int = 0
     n_value_heads: int = 0
     value_dim: int = 0
+    values_are_keys: bool = False
 
     @property
     def v_heads(self) -> int:
@@ -112,6 +115,9 @@ class LayerSpec:
     feed_forward_norm: Optional[PartSpec] = None
     arrangement: str = "pre_norm"
     extra: Tuple[Tuple[str, str, PartSpec], ...] = ()
+    # constants of the arrangement itself (a multiplier on what a sublayer adds to the residual stream, ...),
+    # handed to its factory by name
+    arrangement_params: Tuple[Tuple[str, Any], ...] = ()
 
     def parts(self) -> List[Tuple[str, str, PartSpec]]:
         """(role, family, spec) of every part the layer has."""
@@ -169,7 +175,7 @@ _REGISTRIES: Dict[str, Dict[str, Callable[..., Any]]] = {
 def register_part(family: str, kind: str, factory: Callable[..., Any]) -> None:
     """`factory(**params, dtype=..., device=...)` builds the part.  `family` is
     one of mixer, feed_forward, norm, position, transform, connection; an arrangement's
-    factory takes `(parts, hidden_size, dtype)`."""
+    factory takes `(parts, hidden_size, dtype)` and, by name, the layer's `arrangement_params`."""
     if family not in _REGISTRIES:
         raise KeyError(f"unknown family '{family}' (have {sorted(_REGISTRIES)})")
     _REGISTRIES[family][kind] = factory
@@ -230,6 +236,13 @@ class Norm(Part):
         """The norm of sum_s weights[s] * x[:, s] for x float32 [rows, streams * width] (weights None: the plain
         sum); `clear`: a float32 [rows, width] tensor set to zero by the same launch, `clear2`: a float32 scratch
         tensor of the part that runs next, zeroed besides.  Needed only by models with several residual streams."""
+        raise NotImplementedError
+
+    def add_normed(self, y: Optional[torch.Tensor], residual: torch.Tensor, mult: float,
+                   x_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+        """residual += mult * norm(y) for a sublayer's float32 output y (set to zero afterwards), then
+        x_out = residual in x_out's dtype, in one launch; `clear` as in `forward`.  Needed only by arrangements
+        that norm a sublayer's output instead of its input."""
         raise NotImplementedError
 
 

@@ -137,7 +137,8 @@ class GatedLinear:
     """out = silu(x Wg^T) * (x Wu^T) with Wg stacked over Wu
     (crates/janus-engine/src/model/block.rs:383-430).  With `limit` > 0 the activation is the clamped form
     g * sigmoid(alpha g) * (u + 1), g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), in the same places:
-    the product's own epilogue, or the activation kernel behind a plain product."""
+    the product's own epilogue, or the activation kernel behind a plain product.  A negative `limit`
+    (`ops.GELU_TANH_GATE`) makes the activation the tanh form of GELU on the gate: gelu_tanh(x Wg^T) * (x Wu^T)."""
 
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device,
                  name: str = "gate_up", limit: float = 0.0, alpha: float = 1.0, pad_width: bool = False):
@@ -170,7 +171,7 @@ class GatedLinear:
         if self.dtype == torch.float32:
             gu = ctx.workspace.get("gate_up", (x.shape[0], 2 * self.out_features), torch.float32)
             ops.gemm_f32(x, self.weight, gu, accumulate=False, label=self.name)
-            if self.limit > 0.0:
+            if self.limit != 0.0:
                 ops.clamped_glu(gu, out, self.out_features, self.limit, self.alpha)
             else:
                 ops.swiglu(gu, out)
@@ -180,7 +181,7 @@ class GatedLinear:
                 self._stacked = self.weight.stacked()
             gu = ctx.workspace.get("gate_up", (x.shape[0], self._stacked.rows), torch.float32)
             ops.gemm_bf16(x, self._stacked, gu, mode="store", pair=False, label=self.name)
-            if self.limit > 0.0:
+            if self.limit != 0.0:
                 ops.clamped_glu(gu, out, 128 * self.weight.up_tile_offset, self.limit, self.alpha)
             else:
                 ops.swiglu_f32_to_bf16(gu, out, 128 * self.weight.up_tile_offset)

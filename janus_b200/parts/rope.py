@@ -117,6 +117,39 @@ class RampedRotaryEncoding(RotaryEncoding):
         return self._table
 
 
+class BandScaledRotaryEncoding(RotaryEncoding):
+    """Rotary positions on the first `dims` dimensions of a vector (the mixer passes the rest through), pair
+    (i, i + dims/2) at frequency theta^(-2i/dims); with `scaling` (factor, low, high, original) the frequencies are
+    scaled band by band as `llama3_scaled` does (long waves divided by the factor, short ones kept, a linear blend
+    between).  Frequencies, angles, cos and sin are made on the host in float64 and rounded to float32 once."""
+
+    def __init__(self, dims: int, theta: float, max_positions: int, scaling: Optional[dict] = None,
+                 dtype: torch.dtype = torch.float32, device: torch.device = torch.device("cpu")):
+        super().__init__(dims, theta, max_positions, None, dtype, device)
+        self.dims = int(dims)
+        f = torch.pow(torch.tensor(float(theta), dtype=torch.float64),
+                      -torch.arange(0, dims, 2, dtype=torch.float64) / float(dims))
+        if scaling is not None:
+            factor, low, high = float(scaling["factor"]), float(scaling["low"]), float(scaling["high"])
+            original = float(scaling["original"])
+            wavelen = (2.0 * math.pi) / f
+            if high == low:
+                blended = f / factor
+            else:
+                smooth = (original / wavelen - low) / (high - low)
+                blended = (1.0 - smooth) * f / factor + smooth * f
+            f = torch.where(wavelen < original / high, f, torch.where(wavelen > original / low, f / factor, blended))
+        self.inv_freq = f
+
+    @property
+    def table(self) -> torch.Tensor:
+        if self._table is None:
+            angle = torch.arange(self._limit, dtype=torch.float64)[:, None] * self.inv_freq.to(torch.float64)[None, :]
+            self._table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).to(torch.float32).contiguous() \
+                .to(self.device)
+        return self._table
+
+
 class NoPositions(PositionEncoding):
     """A mixer whose order information comes from elsewhere."""
 
@@ -129,4 +162,5 @@ class NoPositions(PositionEncoding):
 
 register_part("position", "rotary", RotaryEncoding)
 register_part("position", "ramped_rotary", RampedRotaryEncoding)
+register_part("position", "band_rotary", BandScaledRotaryEncoding)
 register_part("position", "none", NoPositions)
