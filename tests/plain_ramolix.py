@@ -257,3 +257,82 @@ class PlainRamolix:
                 after.append(x.clone())
         logits = rms_norm(x, w["final.norm"], eps) @ w["embed"].T
         return (logits, torch.stack(after)) if keep_layers else logits
+
+
+def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int]) -> torch.Tensor:
+    """The logits [T, vocab] of a whole sequence."""
+    return PlainRamolix(cfg, w).forward(0, ids)
+
+
+def forward_in_pieces(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int], cuts: List[int]) -> torch.Tensor:
+    """The same logits with the sequence fed piece by piece (`cuts`: piece lengths) through the states."""
+    m = PlainRamolix(cfg, w)
+    out, at = [], 0
+    for n in cuts:
+        out.append(m.forward(0, ids[at:at + n]))
+        at += n
+    return torch.cat(out)
+
+
+# ---------------------------------------------------------------------------------------------
+# random models
+# ---------------------------------------------------------------------------------------------
+def random_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
+    """Random tensors for a configuration, rounded to bfloat16 values (as a stored model's are)."""
+    g = torch.Generator().manual_seed(seed)
+    W = int(cfg["width"])
+
+    def rnd(*shape, s=1.0, mean=0.0):
+        return (torch.randn(*shape, generator=g) * s + mean).to(torch.bfloat16).to(DT)
+
+    w = {"embed": rnd(cfg["vocab"], W), "final.norm": rnd(W, s=0.1, mean=1.0)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        w[p + "norm1"] = rnd(W, s=0.1, mean=1.0)
+        if layer["type"] == "attention":
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            w[p + "mix.q"], w[p + "mix.k"] = rnd(H * d, W, s=W ** -0.5), rnd(G * d, W, s=W ** -0.5)
+            w[p + "mix.q.b"], w[p + "mix.k.b"] = rnd(H * d, s=0.2), rnd(G * d, s=0.2)
+            w[p + "mix.q.norm"], w[p + "mix.k.norm"] = rnd(H * d, s=0.2, mean=1.0), rnd(G * d, s=0.2, mean=1.0)
+            w[p + "mix.o"] = rnd(W, H * d, s=(H * d) ** -0.5)
+        elif layer["type"] == "latent_attention":
+            H, d, e, r = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+            w[p + "mix.q"] = rnd(H * d, W, s=W ** -0.5)
+            if m.get("kv_from") is None:
+                w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = rnd(r, W, s=W ** -0.5), rnd(r, s=0.2, mean=1.0)
+            w[p + "mix.uk"], w[p + "mix.uv"] = rnd(H * d, r, s=r ** -0.5), rnd(H * e, r, s=r ** -0.5)
+            w[p + "mix.o"] = rnd(W, H * e, s=(H * e) ** -0.5)
+        else:
+            H, P, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            inner, C = H * P, H * P + 2 * G * N
+            w[p + "mix.in"] = rnd(2 * inner + 2 * G * N + H, W, s=W ** -0.5)
+            w[p + "mix.conv"], w[p + "mix.conv.b"] = rnd(C, taps, s=taps ** -0.5), rnd(C, s=0.2)
+            w[p + "mix.dt_bias"], w[p + "mix.A_log"] = rnd(H, s=0.7), rnd(H, s=0.7, mean=-1.0)
+            w[p + "mix.D"], w[p + "mix.norm"] = rnd(H, s=0.3, mean=1.0), rnd(inner, s=0.1, mean=1.0)
+            w[p + "mix.o"] = rnd(W, inner, s=inner ** -0.5)
+        if layer.get("mlp") is not None:
+            F = layer["mlp"]["ff"]
+            w[p + "norm2"] = rnd(W, s=0.1, mean=1.0)
+            w[p + "mlp.gate"], w[p + "mlp.up"] = rnd(F, W, s=W ** -0.5), rnd(F, W, s=W ** -0.5)
+            w[p + "mlp.down"] = rnd(W, F, s=F ** -0.5)
+    return w
+
+
+def save_folder(cfg: dict, w: Dict[str, torch.Tensor], out_dir: str, dtype=torch.bfloat16) -> str:
+    """Write config.json and model.safetensors (an independent writer of the file format)."""
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, at = {}, [], 0
+    names = {torch.bfloat16: "BF16", torch.float32: "F32"}
+    for name, t in w.items():
+        t = t.to(dtype).contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": names[dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(os.path.join(out_dir, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+    return out_dir
