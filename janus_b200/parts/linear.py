@@ -88,6 +88,8 @@ class Linear:
         float32 engine uses the embedding's storage as it is, the bfloat16 engine a packed copy)."""
         if tuple(w.shape) != (self.out_features, self.in_features):
             raise ValueError(f"weight of shape {tuple(w.shape)} does not fit ({self.out_features}, {self.in_features})")
+        if self._padded is not None:
+            w = self._padded.weight(w)
         self.weight = ops.pack_weight(w) if self.dtype == torch.bfloat16 else w
 
     def first_rows(self, rows: int) -> "Linear":
