@@ -94,7 +94,8 @@ class Linear:
 
     def first_rows(self, rows: int) -> "Linear":
         """The product with the first `rows` output features only (shares storage)."""
-        sub = Linear(self.in_features, rows, self.dtype, self.device, self.name)
+        sub = Linear(self.in_features, rows, self.dtype, self.device, self.name, pad_width=self._padded is not None)
+        sub._padded = self._padded          # the same padded copies of the rows serve both
         sub.weight = self.weight.first_rows(rows) if self.dtype == torch.bfloat16 else self.weight[:rows]
         return sub
 
