@@ -21,7 +21,8 @@ the same weights (`checked`).
 
 Other modes (one JSON line per item, none of them the headline): --kernels,
 --prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline, --float32, --design
-(the Zivitar design beside the Llama decoder at equal layer sizes: prompt and decode throughput, a step's kernels).
+(the Zivitar design, or with --design-model ramolix the Ramolix design, beside the Llama decoder at equal layer
+sizes: prompt and decode throughput, a step's kernels).
 """
 import argparse
 import json
@@ -664,6 +665,20 @@ def zivitar_config(width, ff, heads, kv_heads, window, vocab):
                 logit_softcap=30.0, layers=[lightning, attention, attention, attention])
 
 
+def ramolix_config(width, ff, heads, kv_heads, window, vocab):
+    """Four layers at the size's width: two state-space mixers (inner width twice the model's, heads of 64 values,
+    128 state rows, one group, four taps), sliding-window attention whose values are its keys (head size 128, half
+    of it rotated) and latent attention (128 per head, latents of 256), each with a GELU-gated feed-forward."""
+    mlp = dict(kind="dense", ff=ff)
+    mamba = dict(type="mamba2", mlp=mlp, mixer=dict(heads=2 * width // 64, vdim=64, state=128, groups=1, conv=4, norm_groups=1))
+    attention = dict(type="attention", mlp=mlp,
+                     mixer=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=window),
+                                rot=dict(dims=64, base=10000.0, scaling=dict(factor=4.0, low=1.0, high=4.0, original=4096))))
+    latent = dict(type="latent_attention", mlp=mlp, mixer=dict(heads=heads, dim=128, vdim=128, kv_rank=256, scale=128 ** -0.5))
+    return dict(architecture="Ramolix", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=width ** 0.5),
+                residual_mult=0.7, layers=[mamba, attention, mamba, latent])
+
+
 def llama_like(width, ff, heads, kv_heads, window, vocab):
     return dict(architectures=["LlamaForCausalLM"], hidden_size=width, num_hidden_layers=4, num_attention_heads=heads,
                 num_key_value_heads=kv_heads, head_dim=128, intermediate_size=ff, vocab_size=vocab,
@@ -671,9 +686,12 @@ def llama_like(width, ff, heads, kv_heads, window, vocab):
                 tie_word_embeddings=False)
 
 
-def run_design(which):
-    """The Zivitar design beside the Llama decoder at equal layer sizes (random weights, four layers): prompt
-    steps and decode steps timed on the device, and each step's kernels one by one (`Model.profile`).  One
+DESIGNS = {"zivitar": zivitar_config, "ramolix": ramolix_config}
+
+
+def run_design(which, design="zivitar"):
+    """A design (Zivitar or Ramolix) beside the Llama decoder at equal layer sizes (random weights, four layers):
+    prompt steps and decode steps timed on the device, and each step's kernels one by one (`Model.profile`).  One
     JSON line per (size, model)."""
     import torch
 
@@ -681,7 +699,7 @@ def run_design(which):
     from janus_b200.engine.step import StepEntry
     for name in which.split(","):
         size = DESIGN_SIZES[name]
-        for label, cfg in (("zivitar", zivitar_config(**size)), ("llama", llama_like(**size))):
+        for label, cfg in ((design, DESIGNS[design](**size)), ("llama", llama_like(**size))):
             model = janus_b200.load_random(cfg, seed=5, dtype="bfloat16", max_tokens=8 * 2176 + 8192 + 1024, max_slots=16,
                                            max_seq_len=16384, norm_std=0.0)
             V = size["vocab"]
@@ -887,8 +905,10 @@ def main():
                     help="time the plain implementation of tests/ on the host (the only runnable stand-in for the "
                          "reference on this box): Tiny A, Tiny B and one 8B-sized layer (one JSON line each)")
     ap.add_argument("--design", nargs="?", const="2k,4k", default=None, metavar="SIZE,...",
-                    help="the Zivitar design beside the Llama decoder at equal layer sizes (" + ", ".join(DESIGN_SIZES) +
+                    help="a second design beside the Llama decoder at equal layer sizes (" + ", ".join(DESIGN_SIZES) +
                          "): prompt and decode throughput and each step's kernels, one JSON line per size and model")
+    ap.add_argument("--design-model", choices=sorted(DESIGNS), default="zivitar",
+                    help="which design --design measures (default: zivitar)")
     args = ap.parse_args()
     if args.cpu_baseline:
         run_cpu_baseline()
@@ -914,7 +934,7 @@ def main():
         run_plan_check()
         return 0
     if args.design:
-        run_design(args.design)
+        run_design(args.design, args.design_model)
         return 0
     if args.prompt_lengths:
         run_prompt_lengths(args.layers or 8, args.prompt_lengths)
