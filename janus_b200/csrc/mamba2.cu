@@ -96,10 +96,14 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kerne
     int tiles_per_seq, float* __restrict__ scratch, float* __restrict__ seg_decay) {
   constexpr int phase = PHASE;
   constexpr int DP = PARTS * RMAX;         // padded rows
-  extern __shared__ __align__(16) float smem[];          // B [CT][DP], C [CT][DP], x [CT][EB], dt [CT], a [CT]
+  // a part's rows start four floats after the part before ends: the four parts of a column read their 16 bytes
+  // from different banks (with the parts RMAX floats apart, a multiple of 32, all four would meet in one)
+  constexpr int PS = RMAX + 4;             // floats from part to part
+  constexpr int TS = PARTS * PS;           // floats from token to token
+  extern __shared__ __align__(16) float smem[];          // B [CT][TS], C [CT][TS], x [CT][EB], dt [CT], a [CT]
   float* b_s = smem;
-  float* c_s = b_s + CT * DP;
-  float* x_s = c_s + CT * DP;
+  float* c_s = b_s + CT * TS;
+  float* x_s = c_s + CT * TS;
   float* dt_s = x_s + CT * EB;
   float* a_s = dt_s + CT;
   jb::pdl_launch_dependents();
@@ -134,8 +138,9 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kerne
       const int tt = idx / DP, r = idx % DP;
       const bool in = r < N;
       const float* row = xbc + (size_t)(c0 + tt) * ldx + (size_t)g * N + (in ? r : 0);
-      b_s[idx] = in ? row[b_col] : 0.0f;
-      if (phase != LOCAL) c_s[idx] = in ? row[c_col] : 0.0f;
+      const int at = tt * TS + (r / RMAX) * PS + r % RMAX;
+      b_s[at] = in ? row[b_col] : 0.0f;
+      if (phase != LOCAL) c_s[at] = in ? row[c_col] : 0.0f;
     }
     for (int idx = threadIdx.x; idx < CT * EB; idx += THREADS) {
       const int tt = idx / EB, c = idx % EB;
@@ -151,8 +156,8 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kerne
       const float a = a_s[tt], dt = dt_s[tt];
       const float2 x = *reinterpret_cast<const float2*>(x_s + tt * EB + 2 * col);
       const float v0 = dt * x.x, v1 = dt * x.y;
-      const float4* cr = reinterpret_cast<const float4*>(c_s + tt * DP + part * RMAX);
-      const float4* br = reinterpret_cast<const float4*>(b_s + tt * DP + part * RMAX);
+      const float4* cr = reinterpret_cast<const float4*>(c_s + tt * TS + part * PS);
+      const float4* br = reinterpret_cast<const float4*>(b_s + tt * TS + part * PS);
       float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
       if (phase == LOCAL) decay_all *= a;
 #pragma unroll
@@ -294,7 +299,7 @@ JB_EXPORT int jb_mamba2_scan(const float* xbc, int ldx, int b_col, int c_col, co
   JB_REFUSE(G < 1 || H % G != 0, "mamba2_scan: %d heads are not a multiple of %d groups", H, G);
   JB_REFUSE(seg_len > 0 && (scratch == nullptr || seg_decay == nullptr), "mamba2_scan: segments need scratch");
   const int rmax = N <= 64 ? 16 : N <= 128 ? 32 : 64;
-  const size_t smem = (size_t)(2 * CT * PARTS * rmax + CT * EB + 2 * CT) * sizeof(float);
+  const size_t smem = (size_t)(2 * CT * PARTS * (rmax + 4) + CT * EB + 2 * CT) * sizeof(float);
   const bool segmented = seg_len > 0;
   const int tiles = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
   const int seg = segmented ? seg_len : 0x40000000;
