@@ -8,7 +8,9 @@
 //   q <- q / sqrt(mean(q^2) + eps) * wq               (one root mean square over all H d numbers), k likewise
 //   the first `rot` dimensions of every head of q and k are turned in the pairing (i, i + rot/2) by the angle
 //   of the token's position (cos and sin from a table [positions][rot/2][2]); the rest pass
-//   q is written [T, H d] in the engine dtype, k is appended to the key pages.
+//   q is written [T, H dp] in the engine dtype, k is appended to the key pages; dp >= d is the size a head is
+//   stored with (a head size that the attention kernel does not take is stored as the next size it takes, the
+//   extra columns zero: scores and sums do not change).
 //
 // latent_prep (latent attention, queries already multiplied into the latent space):
 //   q = proj[:, 0 : Q] written [T, Q] in the engine dtype
@@ -30,7 +32,8 @@ __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, int ld
                                           const float* __restrict__ wk, float eps, const float* __restrict__ table,
                                           int rot, const int* __restrict__ positions, TO* __restrict__ q_out,
                                           const int* __restrict__ dest, TO* __restrict__ k_cache,
-                                          TO* __restrict__ v_cache, int H, int G, int d, int page_size, int write_kv) {
+                                          TO* __restrict__ v_cache, int H, int G, int d, int dp, int page_size,
+                                          int write_kv) {
   extern __shared__ __align__(16) float row_s[];     // q [H d], then k [G d]
   __shared__ float scratch[33];
   jb::pdl_launch_dependents();
@@ -55,7 +58,7 @@ __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, int ld
       if (bk != nullptr) v += bk[c];
       sk += v * v;
       const int g = c / d, j = c % d;
-      v_cache[((page * G + g) * page_size + prow) * d + j] = jb::from_f32<TO>(v);
+      v_cache[((page * G + g) * page_size + prow) * dp + j] = jb::from_f32<TO>(v);
     }
     row_s[i] = v;
   }
@@ -75,8 +78,8 @@ __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, int ld
     const int head = c / d, j = c % d;
     const float* w = is_q ? wq : wk;
     const float r = is_q ? rq : rk;
-    TO* out = is_q ? q_out + (size_t)t * QW + (size_t)head * d
-                   : k_cache + ((page * G + head) * page_size + prow) * d;
+    TO* out = is_q ? q_out + ((size_t)t * H + head) * dp
+                   : k_cache + ((page * G + head) * page_size + prow) * dp;
     if (cs != nullptr && j < rot) {
       if (j >= half) continue;                       // written by the thread of the pair's first member
       const float u = (row_s[i] / r) * w[c], v = (row_s[i + half] / r) * w[c + half];
@@ -87,10 +90,14 @@ __global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, int ld
       out[j] = jb::from_f32<TO>((row_s[i] / r) * w[c]);
     }
   }
+  // heads stored wider than they are: the queries' extra columns are zero (those of the pages are never written)
+  const int extra = dp - d;
+  for (int i = threadIdx.x; i < H * extra; i += blockDim.x)
+    q_out[((size_t)t * H + i / extra) * dp + d + i % extra] = jb::from_f32<TO>(0.0f);
 }
 
 template <typename TO>
-__global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int Q, int r, const float* __restrict__ w,
+__global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int Q, int r, int rp, const float* __restrict__ w,
                                    float eps, TO* __restrict__ q_out, const int* __restrict__ dest,
                                    TO* __restrict__ c_cache, int write_c) {
   __shared__ float scratch[33];
@@ -104,20 +111,21 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int Q
   for (int i = threadIdx.x; i < r; i += blockDim.x) ss += pr[Q + i] * pr[Q + i];
   ss = jb::block_sum(ss, scratch);
   const float rms = sqrtf(ss / (float)r + eps);
-  TO* out = c_cache + (size_t)dest[t] * r;          // one key head: row dest[t] of [page * page_size][r]
+  TO* out = c_cache + (size_t)dest[t] * rp;         // one key head: row dest[t] of [page * page_size][rp]
   for (int i = threadIdx.x; i < r; i += blockDim.x) out[i] = jb::from_f32<TO>((pr[Q + i] / rms) * w[i]);
 }
 
 }  // namespace
 
 // proj: float32 [T, ld]; bq [H d], bk [G d] (either may be null), wq [H d], wk [G d] float32; table: float32
-// [positions][rot/2][2] or null (no rotation); q_out [T, H d] and the pages in out_dtype.  write_kv = 0: q only
+// [positions][rot/2][2] or null (no rotation); q_out [T, H dp] and the pages (rows of dp) in out_dtype.  write_kv = 0: q only
 // (a place that reads the keys and values another place wrote).
 JB_EXPORT int jb_qk_norm_rope_cache(const float* proj, int ld, const float* bq, const float* bk, const float* wq,
                                     const float* wk, float eps, const float* table, int rot, const int* positions,
                                     void* q_out, int out_dtype, const int* dest, void* k_cache, void* v_cache, int T,
-                                    int H, int G, int d, int page_size, int write_kv, cudaStream_t stream) {
+                                    int H, int G, int d, int dp, int page_size, int write_kv, cudaStream_t stream) {
   if (T <= 0) return 0;
+  JB_REFUSE(dp < d, "qk_norm_rope_cache: heads of %d cannot be stored in %d columns", d, dp);
   JB_REFUSE(rot < 0 || rot > d || (rot & 1), "qk_norm_rope_cache: %d rotated dimensions do not fit a head of %d", rot, d);
   JB_REFUSE(ld < (H + (write_kv ? G : 0)) * d, "qk_norm_rope_cache: rows of %d floats do not hold the projections", ld);
   const size_t smem = (size_t)(H + (write_kv ? G : 0)) * d * sizeof(float);
@@ -131,7 +139,7 @@ JB_EXPORT int jb_qk_norm_rope_cache(const float* proj, int ld, const float* bq, 
       if (e != cudaSuccess) return (int)e;                                                                             \
     }                                                                                                                  \
     e = cudaLaunchKernelEx(&cfg.c, qk_norm_rope_cache_kernel<TO>, proj, ld, bq, bk, wq, wk, eps, table, rot,           \
-                           positions, (TO*)q_out, dest, (TO*)k_cache, (TO*)v_cache, H, G, d, page_size, write_kv);    \
+                           positions, (TO*)q_out, dest, (TO*)k_cache, (TO*)v_cache, H, G, d, dp, page_size, write_kv);\
   } while (0)
   if (out_dtype == JB_F32) JB_LAUNCH_QK(float);
   else if (out_dtype == JB_BF16) JB_LAUNCH_QK(bf16);
@@ -141,18 +149,19 @@ JB_EXPORT int jb_qk_norm_rope_cache(const float* proj, int ld, const float* bq, 
 }
 
 // proj: float32 [T, ld] with the queries in columns [0, Q) and the latent projection in [Q, Q + r); w [r] float32;
-// q_out [T, Q] and the pages ([page][1][page_size][r]) in out_dtype.  write_c = 0: queries only.
-JB_EXPORT int jb_latent_prep(const float* proj, int ld, int Q, int r, const float* w, float eps, void* q_out,
+// q_out [T, Q] and the pages ([page][1][page_size][rp], rp >= r the size a row is stored with, extra columns never
+// written) in out_dtype.  write_c = 0: queries only.
+JB_EXPORT int jb_latent_prep(const float* proj, int ld, int Q, int r, int rp, const float* w, float eps, void* q_out,
                              int out_dtype, const int* dest, void* c_cache, int T, int write_c, cudaStream_t stream) {
   if (T <= 0) return 0;
-  JB_REFUSE(ld < Q + (write_c ? r : 0), "latent_prep: rows of %d floats do not hold the projections", ld);
+  JB_REFUSE(ld < Q + (write_c ? r : 0) || rp < r, "latent_prep: rows of %d floats do not hold the projections", ld);
   jb::Launch cfg(dim3(T), dim3(256), 0, stream);
   cudaError_t e;
   if (out_dtype == JB_F32)
-    e = cudaLaunchKernelEx(&cfg.c, latent_prep_kernel<float>, proj, ld, Q, r, w, eps, (float*)q_out, dest,
+    e = cudaLaunchKernelEx(&cfg.c, latent_prep_kernel<float>, proj, ld, Q, r, rp, w, eps, (float*)q_out, dest,
                            (float*)c_cache, write_c);
   else if (out_dtype == JB_BF16)
-    e = cudaLaunchKernelEx(&cfg.c, latent_prep_kernel<bf16>, proj, ld, Q, r, w, eps, (bf16*)q_out, dest,
+    e = cudaLaunchKernelEx(&cfg.c, latent_prep_kernel<bf16>, proj, ld, Q, r, rp, w, eps, (bf16*)q_out, dest,
                            (bf16*)c_cache, write_c);
   else
     return JB_ERR_BAD_DTYPE;

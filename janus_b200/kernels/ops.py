@@ -69,8 +69,8 @@ _SIGNATURES = {
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
     "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
     "jb_clamped_glu": "piipiiiffp",
-    "jb_sublayer_norm_add": "ppiffppiiiplp", "jb_qk_norm_rope_cache": "pippppfpippipppiiiiiip",
-    "jb_latent_prep": "piiipfpippiip", "jb_causal_conv_silu": "piiippipllppppiiip",
+    "jb_sublayer_norm_add": "ppiffppiiiplp", "jb_qk_norm_rope_cache": "pippppfpippipppiiiiiiip",
+    "jb_latent_prep": "piiiipfpippiip", "jb_causal_conv_silu": "piiippipllppppiiip",
     "jb_mamba2_scan": "piiipipppppllppiiiiiiippp", "jb_gated_group_rmsnorm": "ppipfpiiiip", "jb_pad_rows_bf16": "pipiip", "jb_scale_softcap": "plffp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
@@ -1177,16 +1177,18 @@ def qk_norm_rope_cache(proj: torch.Tensor, bq: Optional[torch.Tensor], bk: Optio
                        wk: torch.Tensor, eps: float, table: Optional[torch.Tensor], rot: int, positions: torch.Tensor,
                        q_out: torch.Tensor, dest: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
                        v_cache: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, page_size: int,
-                       write_kv: bool = True) -> None:
+                       write_kv: bool = True, stored_dim: Optional[int] = None) -> None:
     """proj float32 [T, >= (heads + kv_heads) dim]: q and k as projected.  Adds the biases, appends k (with its bias,
     before norm and rotation) to the value pages, norms q and k each over its whole row, turns the first `rot`
     dimensions of every head by the table's cos and sin at the token's position, writes q [T, heads dim] and
-    appends k to the key pages.  write_kv False: q alone."""
+    appends k to the key pages.  write_kv False: q alone.  `stored_dim` >= dim: the size a head has in q and in the
+    pages (extra columns zero)."""
     T = q_out.shape[0]
+    dp = dim if stored_dim is None else int(stored_dim)
     _need(proj, "projections", torch.float32)
     if proj.shape[0] != T:
         raise KernelError("qk_norm_rope_cache: projections and queries differ in their rows")
-    _need(q_out, "q_out", None, (T, heads * dim))
+    _need(q_out, "q_out", None, (T, heads * dp))
     _need(wq, "q norm weight", torch.float32, (heads * dim,))
     _need(positions, "positions", torch.int32, (T,))
     if bq is not None:
@@ -1206,16 +1208,18 @@ def qk_norm_rope_cache(proj: torch.Tensor, bq: Optional[torch.Tensor], bk: Optio
         _ptr(proj), proj.shape[1], _ptr(bq), _ptr(bk) if write_kv else None, _ptr(wq), _ptr(wk) if write_kv else None,
         eps, _ptr(table) if rot > 0 else None, int(rot), _ptr(positions), _ptr(q_out), dtype_code(q_out.dtype),
         _ptr(dest) if write_kv else None, _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None,
-        T, heads, kv_heads, dim, page_size, int(write_kv), _stream()), "qk_norm_rope_cache")
+        T, heads, kv_heads, dim, dp, page_size, int(write_kv), _stream()), "qk_norm_rope_cache")
 
 
 def latent_prep(proj: torch.Tensor, q_width: int, rank: int, weight: Optional[torch.Tensor], eps: float,
                 q_out: torch.Tensor, dest: Optional[torch.Tensor], c_cache: Optional[torch.Tensor],
-                write_c: bool = True) -> None:
+                write_c: bool = True, stored_rank: Optional[int] = None) -> None:
     """proj float32 [T, >= q_width (+ rank)]: q_out = the first q_width columns in q_out's dtype; the next `rank`
     columns, divided by their root mean square and multiplied by `weight`, are appended to the pages as the token's
-    key row (one key head of size rank).  write_c False: the queries alone."""
+    key row (one key head of size rank, stored in rows of `stored_rank` >= rank columns).  write_c False: the
+    queries alone."""
     T = q_out.shape[0]
+    rp = rank if stored_rank is None else int(stored_rank)
     _need(proj, "projections", torch.float32)
     if proj.shape[0] != T:
         raise KernelError("latent_prep: projections and queries differ in their rows")
@@ -1225,7 +1229,7 @@ def latent_prep(proj: torch.Tensor, q_width: int, rank: int, weight: Optional[to
         _need(dest, "cache rows", torch.int32, (T,))
         _need(c_cache, "latent pages", q_out.dtype)
     _check(_lib("qk_prep").jb_latent_prep(
-        _ptr(proj), proj.shape[1], int(q_width), int(rank), _ptr(weight) if write_c else None, eps, _ptr(q_out),
+        _ptr(proj), proj.shape[1], int(q_width), int(rank), rp, _ptr(weight) if write_c else None, eps, _ptr(q_out),
         dtype_code(q_out.dtype), _ptr(dest) if write_c else None, _ptr(c_cache) if write_c else None, T, int(write_c),
         _stream()), "latent_prep")
 

@@ -41,6 +41,13 @@ def _check_kernel_limits(num_heads: int, num_kv_heads: int, head_dim: int, dtype
                              f"{head_dim} (at most {ops.ATTENTION_BF16_MAX_GROUP}); such a model runs with dtype float32")
 
 
+def stored_head_size(size: int, dtype: torch.dtype) -> int:
+    """The size a head of `size` numbers is stored with in queries and pages so that the attention kernels take it:
+    the bfloat16 kernels read rows in 16-byte pieces, so a size that is no multiple of 8 is stored as the next one,
+    the extra columns zero (neither the scores nor the weighted sums change)."""
+    return (size + 7) // 8 * 8 if dtype == torch.bfloat16 else size
+
+
 def attend_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, ctx, group,
                  num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
     """Causal attention of the step's queries (engine dtype, already in their final form) over pages that already

@@ -21,7 +21,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .attention import _check_kernel_limits, attend_paged
+from .attention import _check_kernel_limits, attend_paged, stored_head_size
 from .base import KVSpec, Mixer, register_part
 from .linear import Linear
 
@@ -34,8 +34,11 @@ class LatentAttention(Mixer):
                                                                       int(vdim), int(rank))
         self.scale, self.eps, self.own_latent = float(scale), float(eps), bool(own_latent)
         self.dtype, self.device = dtype, device
-        _check_kernel_limits(self.nh, 1, self.rank, dtype)       # the attention runs with head size rank, one kv head
-        self.q_width = self.nh * self.rank
+        # the attention runs with head size rank and one kv head (a rank that the bfloat16 kernels do not take is
+        # stored as the next size they take: zero rows in the queries' matrix, zero columns in the output's)
+        self.rank_stored = stored_head_size(self.rank, dtype)
+        _check_kernel_limits(self.nh, 1, self.rank_stored, dtype)
+        self.q_width = self.nh * self.rank_stored
         # rows: the queries in latent space, then (own latent) the latent's projection
         self.proj = Linear(hidden_size, self.q_width + (self.rank if self.own_latent else 0), dtype, device,
                            name="q_dkv" if self.own_latent else "q", pad_width=True)
@@ -44,7 +47,7 @@ class LatentAttention(Mixer):
         self.norm_weight: Optional[torch.Tensor] = None
 
     def cache_spec(self) -> Optional[KVSpec]:
-        return KVSpec(1, self.rank, values_are_keys=True) if self.own_latent else None
+        return KVSpec(1, self.rank_stored, values_are_keys=True) if self.own_latent else None
 
     def weight_shapes(self):
         shapes = {"q": ((self.nh * self.dim, self.hidden_size), "normal"),
@@ -61,9 +64,14 @@ class LatentAttention(Mixer):
                 raise ValueError(f"weight '{name}' of shape {tuple(t.shape)} does not fit {shape}")
         f64 = lambda t: t.to(device=self.device, dtype=torch.float64)      # noqa: E731
         # queries into latent space: rows [head][rank] = Wuk_h^T Wq_h
-        q_latent = torch.einsum("hdr,hdw->hrw", f64(uk).view(H, d, r), f64(q).view(H, d, W)).reshape(H * r, W)
+        rp = self.rank_stored
+        q_latent = torch.zeros((H, rp, W), dtype=torch.float64, device=self.device)
+        q_latent[:, :r] = torch.einsum("hdr,hdw->hrw", f64(uk).view(H, d, r), f64(q).view(H, d, W))
+        q_latent = q_latent.reshape(H * rp, W)
         # the output from latent space: columns [head][rank] = Wo_h Wuv_h
-        o_latent = torch.einsum("whe,her->whr", f64(o).view(W, H, e), f64(uv).view(H, e, r)).reshape(W, H * r)
+        o_latent = torch.zeros((W, H, rp), dtype=torch.float64, device=self.device)
+        o_latent[:, :, :r] = torch.einsum("whe,her->whr", f64(o).view(W, H, e), f64(uv).view(H, e, r))
+        o_latent = o_latent.reshape(W, H * rp)
         if self.own_latent:
             if dkv is None or dkv_norm is None or tuple(dkv_norm.shape) != (r,):
                 raise ValueError("a latent attention layer with a latent of its own needs 'dkv' and 'dkv_norm'")
@@ -98,9 +106,9 @@ class LatentAttention(Mixer):
         lin.forward(x, proj, y_is_zero=scratch_cleared)
         q = ws.get("latent_q", (T, self.q_width), self.dtype)
         ops.latent_prep(proj, self.q_width, self.rank, self.norm_weight, self.eps, q, group.dest_rows, cache_view.k,
-                        write_c=writes_cache)
+                        write_c=writes_cache, stored_rank=self.rank_stored)
         attn = ws.get("latent_attn", (T, self.q_width), self.dtype)
-        attend_paged(q, cache_view.k, cache_view.k, attn, ctx, group, self.nh, 1, self.rank, 0, self.scale)
+        attend_paged(q, cache_view.k, cache_view.k, attn, ctx, group, self.nh, 1, self.rank_stored, 0, self.scale)
         self.o.forward_add(attn, residual)
 
 

@@ -9,7 +9,8 @@ concatenated heads are projected by Wo.
 
 q and k are one stacked product whose float32 accumulators one kernel turns into the queries and the cache rows
 (bias, value append, norm, rotation, key append: `ops.qk_norm_rope_cache`); the attention itself is the library's
-grouped-query attention (keys and values have the same size here).  A window lets the cache give pages back.
+grouped-query attention (keys and values have the same size here; a head size that its bfloat16 kernels do not take is
+stored as the next one they take, with zero columns).  A window lets the cache give pages back.
 """
 from __future__ import annotations
 
@@ -18,7 +19,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .attention import _check_kernel_limits, attend_paged
+from .attention import _check_kernel_limits, attend_paged, stored_head_size
 from .base import KVSpec, Mixer, PartSpec, register_part, shared_part
 from .linear import Linear
 
@@ -34,17 +35,18 @@ class SharedKVAttention(Mixer):
         self.hidden_size, self.nh, self.nkv, self.dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(dim)
         self.scale, self.eps, self.window, self.bias = float(scale), float(eps), int(window), bool(bias)
         self.dtype, self.device = dtype, device
-        _check_kernel_limits(self.nh, self.nkv, self.dim, dtype)
+        self.dim_stored = stored_head_size(self.dim, dtype)
+        _check_kernel_limits(self.nh, self.nkv, self.dim_stored, dtype)
         self.position = shared_part("position", position, dtype, device) if position is not None else None
         self.rotary_dims = int(rotary_dims) if position is not None else 0
         self.q_width, self.k_width = self.nh * self.dim, self.nkv * self.dim
         self.qk = Linear(hidden_size, self.q_width + self.k_width, dtype, device, name="qk", pad_width=True)
         self.q_only: Optional[Linear] = None             # view of the q rows, for places that read another cache
-        self.o = Linear(self.q_width, hidden_size, dtype, device, name="o", pad_width=True)
+        self.o = Linear(self.nh * self.dim_stored, hidden_size, dtype, device, name="o", pad_width=True)
         self.bq = self.bk = self.wq = self.wk = None
 
     def cache_spec(self) -> KVSpec:
-        return KVSpec(self.nkv, self.dim, self.window)
+        return KVSpec(self.nkv, self.dim_stored, self.window)
 
     def limit_positions(self, n: int) -> None:
         limit = getattr(self.position, "limit_positions", None)
@@ -62,6 +64,12 @@ class SharedKVAttention(Mixer):
     def load(self, q, k, q_norm, k_norm, o, q_bias=None, k_bias=None) -> None:
         self.qk.load([q, k])
         self.q_only = self.qk.first_rows(self.q_width)
+        if tuple(o.shape) != (self.hidden_size, self.q_width):
+            raise ValueError(f"weight 'o' of shape {tuple(o.shape)} does not fit ({self.hidden_size}, {self.q_width})")
+        if self.dim_stored != self.dim:          # zero columns where the stored heads have their extra columns
+            wide = torch.zeros((self.hidden_size, self.nh, self.dim_stored), dtype=o.dtype, device=o.device)
+            wide[:, :, : self.dim] = o.view(self.hidden_size, self.nh, self.dim)
+            o = wide.view(self.hidden_size, self.nh * self.dim_stored)
         self.o.load([o])
 
         def f32(t, n):
@@ -91,12 +99,13 @@ class SharedKVAttention(Mixer):
         proj = ws.get("skv_proj", (T, lin.out_features), torch.float32)
         lin.forward(x, proj, y_is_zero=scratch_cleared)
         table = self.position.fused_rotary_table() if self.position is not None else None
-        q = ws.get("q_rot", (T, self.q_width), self.dtype)
+        q = ws.get("q_rot", (T, self.nh * self.dim_stored), self.dtype)
         ops.qk_norm_rope_cache(proj, self.bq, self.bk, self.wq, self.wk, self.eps, table, self.rotary_dims,
                                ctx.positions, q, group.dest_rows, cache_view.k, cache_view.v, self.nh, self.nkv,
-                               self.dim, group.page_size, write_kv=writes_cache)
-        attn = ws.get("attn_out", (T, self.q_width), self.dtype)
-        attend_paged(q, cache_view.k, cache_view.v, attn, ctx, group, self.nh, self.nkv, self.dim, self.window, self.scale)
+                               self.dim, group.page_size, write_kv=writes_cache, stored_dim=self.dim_stored)
+        attn = ws.get("attn_out", (T, self.nh * self.dim_stored), self.dtype)
+        attend_paged(q, cache_view.k, cache_view.v, attn, ctx, group, self.nh, self.nkv, self.dim_stored, self.window,
+                     self.scale)
         self.o.forward_add(attn, residual)
 
 

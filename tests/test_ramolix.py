@@ -114,11 +114,13 @@ CFG_D = config(128, 64, 1e-5, 8.0, 0.8, [
     layer("mamba2", mamba(2, 32, 80, 1, 3, 2), 32),
     layer("latent_attention", latent(4, 16, 32, 64, 0.3), 64),
     layer("attention", attention(2, 2, 64, 0.12, rot=(32, 10000.0, (4.0, 1.0, 16.0, 32))))])
-# widths that are multiples of nothing: the bfloat16 products run on zero-padded operands, loads are scalar
+# sizes that are multiples of nothing: the bfloat16 products run on zero-padded operands, heads and latents are
+# stored with zero columns up to a size the bfloat16 attention kernels take, loads are scalar
 CFG_E = config(75, 36, 1e-5, 2.5, 0.9, [
-    layer("attention", attention(2, 1, 24, 0.3, mask=33, rot=(6, 100.0)), 22),
+    layer("attention", attention(2, 1, 12, 0.3, mask=33, rot=(6, 100.0)), 22),
     layer("mamba2", mamba(3, 5, 7, 1, 3, 3), 13),
-    layer("latent_attention", latent(3, 5, 9, 24, 0.3), 27)])
+    layer("latent_attention", latent(3, 5, 9, 21, 0.3), 27),
+    layer("latent_attention", latent(2, 7, 3, 21, 0.4, kv_from=2))])
 CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
 
 
@@ -331,6 +333,16 @@ def test_query_and_key_preparation_against_the_plain_mixer():
             ops.qk_norm_rope_cache(dev(proj[:, :H * d]), dev(bq), None, dev(wq), None, 1e-5, table, rot, i32(positions), q2,
                                    None, None, None, H, G, d, page, write_kv=False)
             assert torch.equal(q2, qo)
+            # heads stored wider than they are: the same numbers, zeros behind them
+            dp = d + 6
+            kc, vc = torch.zeros(6, G, page, dp, dtype=dtype, device="cuda"), torch.zeros(6, G, page, dp, dtype=dtype, device="cuda")
+            q3 = torch.full((T, H * dp), 7.0, dtype=dtype, device="cuda")
+            ops.qk_norm_rope_cache(dev(proj), dev(bq), dev(bk), dev(wq), dev(wk), 1e-5, table, rot, i32(positions), q3,
+                                   i32(rows), kc, vc, H, G, d, page, stored_dim=dp)
+            q3 = q3.view(T, H, dp)
+            assert torch.equal(q3[:, :, :d].reshape(T, H * d), qo) and float(q3[:, :, d:].abs().sum()) == 0.0
+            assert rel_err(torch.stack([kc[r // page, :, r % page, :d].float().cpu() for r in rows]), want_k) < tol
+            assert float(kc[..., d:].abs().sum()) == 0.0 and float(vc[..., d:].abs().sum()) == 0.0
 
 
 @gpu
@@ -349,6 +361,9 @@ def test_latent_preparation_against_its_formula():
             assert rel_err(qo.float().cpu(), proj[:, :Q]) < tol
             assert rel_err(torch.stack([cache[x // page, 0, x % page].float().cpu() for x in rows]), want) < tol
             assert int((cache != 0).any(dim=-1).sum()) == T
+            wide = torch.zeros(5, 1, page, r + 3, dtype=dtype, device="cuda")
+            ops.latent_prep(dev(proj), Q, r, dev(w), 1e-6, qo, i32(rows), wide, stored_rank=r + 3)
+            assert torch.equal(wide[..., :r], cache) and float(wide[..., r:].abs().sum()) == 0.0
 
 
 def plain_conv(u, w, b, before):
