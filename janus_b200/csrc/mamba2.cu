@@ -46,7 +46,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ proj, int ld, 
                                         const float* __restrict__ w, const float* __restrict__ bias, int taps,
                                         const float* __restrict__ state, long long slot_stride, long long state_off,
                                         const int* __restrict__ token_seq, const int* __restrict__ q_start,
-                                        const int* __restrict__ seq_slot, float* __restrict__ out) {
+                                        const int* __restrict__ seq_slot, float* __restrict__ out, int shift_here) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x;
@@ -54,8 +54,21 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ proj, int ld, 
   if (c >= C) return;
   const int seq = token_seq[t];
   const int s0 = q_start[seq], li = t - s0;
-  const float* st = state + (size_t)seq_slot[seq] * slot_stride + state_off;
+  float* st = const_cast<float*>(state) + (size_t)seq_slot[seq] * slot_stride + state_off;
   float acc = bias != nullptr ? bias[c] : 0.0f;
+  if (shift_here) {
+    // every sequence brings one token: this thread is the only one that touches its channel of the state, so it
+    // also moves the state on (row s takes row s + 1, the last row takes the new input)
+    const float u_new = proj[(size_t)t * ld + col0 + c];
+    for (int j = 0; j < taps - 1; ++j) {
+      const float u = st[(size_t)j * C + c];
+      acc = fmaf(w[(size_t)c * taps + j], u, acc);
+      if (j > 0) st[(size_t)(j - 1) * C + c] = u;
+    }
+    if (taps > 1) st[(size_t)(taps - 2) * C + c] = u_new;
+    out[(size_t)t * C + c] = silu_f(fmaf(w[(size_t)c * taps + taps - 1], u_new, acc));
+    return;
+  }
   for (int j = 0; j < taps; ++j) {
     const int src = li - (taps - 1) + j;
     const float u = src >= 0 ? proj[(size_t)(s0 + src) * ld + col0 + c] : st[(size_t)(taps - 1 + src) * C + c];
@@ -261,19 +274,24 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const fl
 }  // namespace
 
 // out[t, c] = silu(bias[c] + sum_j w[c][j] u[t - taps + 1 + j][c]) over the columns [col0, col0 + C) of proj.
-// update_state != 0: afterwards the state takes the last taps - 1 inputs of every sequence (a second launch).
+// update_state != 0: afterwards the state takes the last taps - 1 inputs of every sequence: a second launch, or, when
+// every sequence brings one token (single_tokens != 0), the same launch.
 JB_EXPORT int jb_causal_conv_silu(const float* proj, int ld, int col0, int C, const float* w, const float* bias, int taps,
                                   float* state, long long slot_stride, long long state_off, const int* token_seq,
                                   const int* q_start, const int* seq_slot, float* out, int T, int n_seqs,
-                                  int update_state, cudaStream_t stream) {
+                                  int update_state, int single_tokens, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(taps < 1 || ld < col0 + C, "causal_conv_silu: %d taps over columns %d..%d of %d", taps, col0, col0 + C, ld);
   JB_REFUSE(taps > 1 && state == nullptr, "causal_conv_silu: a convolution of %d taps needs its state", taps);
   {
     jb::Launch cfg(dim3(T, (C + 127) / 128), dim3(128), 0, stream);
+    JB_REFUSE(single_tokens && T != n_seqs, "causal_conv_silu: %d tokens are not one for each of %d sequences", T, n_seqs);
+    const int shift_here = (update_state && single_tokens) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg.c, causal_conv_silu_kernel, proj, ld, col0, C, w, bias, taps,
-                                       (const float*)state, slot_stride, state_off, token_seq, q_start, seq_slot, out);
+                                       (const float*)state, slot_stride, state_off, token_seq, q_start, seq_slot, out,
+                                       shift_here);
     if (e != cudaSuccess) return (int)e;
+    if (shift_here) return 0;
   }
   if (update_state && taps > 1) {
     jb::Launch cfg(dim3(n_seqs, (C + 127) / 128), dim3(128), 0, stream);

@@ -70,7 +70,7 @@ _SIGNATURES = {
     "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
     "jb_clamped_glu": "piipiiiffp",
     "jb_sublayer_norm_add": "ppiffppiiiplp", "jb_qk_norm_rope_cache": "pippppfpippipppiiiiiiip",
-    "jb_latent_prep": "piiiipfpippiip", "jb_causal_conv_silu": "piiippipllppppiiip",
+    "jb_latent_prep": "piiiipfpippiip", "jb_causal_conv_silu": "piiippipllppppiiiip",
     "jb_mamba2_scan": "piiipipppppllppiiiiiiippp", "jb_gated_group_rmsnorm": "ppipfpiiiip", "jb_pad_rows_bf16": "pipiip", "jb_scale_softcap": "plffp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
@@ -1241,11 +1241,12 @@ MAMBA2_SEGMENT = 128     # tokens of a segment when a long prompt's recurrence r
 def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      taps: int, state: Optional[torch.Tensor], state_off: int, token_seq: torch.Tensor,
                      q_start: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, n_seqs: int,
-                     update_state: bool = True) -> None:
+                     update_state: bool = True, single_tokens: bool = False) -> None:
     """out[t, c] = silu(bias[c] + sum_j weight[c, j] u[t - taps + 1 + j, c]) with u the columns [col0, col0 + channels)
     of proj (float32) within each sequence; the inputs before a step's first token come from `state` (float32
     [slots, n], the convolution's [taps - 1, channels] block at offset state_off of a slot's row), which afterwards
-    takes the sequence's last taps - 1 inputs (a second launch)."""
+    takes the sequence's last taps - 1 inputs: a second launch, or the same one when every sequence brings one token
+    (`single_tokens`)."""
     T = proj.shape[0]
     _need(proj, "projections", torch.float32)
     _need(out, "convolution out", torch.float32, (T, channels))
@@ -1259,11 +1260,14 @@ def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch
     _need(token_seq, "token sequences", torch.int32, (T,))
     _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
     _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
-    two = bool(update_state and taps > 1)
+    if single_tokens and T != n_seqs:
+        raise KernelError("causal_conv_silu: single_tokens needs one token per sequence")
+    two = bool(update_state and taps > 1 and not single_tokens)
     _check(_lib("mamba2").jb_causal_conv_silu(
         _ptr(proj), proj.shape[1], int(col0), int(channels), _ptr(weight), _ptr(bias), int(taps), _ptr(state),
         state.shape[1] if state is not None else 0, int(state_off), _ptr(token_seq), _ptr(q_start), _ptr(seq_slot),
-        _ptr(out), T, n_seqs, int(two), _stream()), "causal_conv_silu", kernels=2 if two else 1)
+        _ptr(out), T, n_seqs, int(bool(update_state)), int(bool(single_tokens)), _stream()), "causal_conv_silu",
+        kernels=2 if two else 1)
 
 
 def mamba2_scan(xbc: torch.Tensor, b_col: int, c_col: int, dt_raw: torch.Tensor, dt_bias: torch.Tensor,

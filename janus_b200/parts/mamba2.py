@@ -95,7 +95,8 @@ class Mamba2Mixer(Mixer):
         self.in_proj.forward(x, proj, y_is_zero=scratch_cleared)
         xbc = ws.get("mamba2_xbc", (T, self.channels), torch.float32)
         ops.causal_conv_silu(proj, self.inner, self.channels, self.conv_w, self.conv_b, self.taps, state,
-                             self.scan_floats, ctx.token_seq, ctx.q_start, ctx.seq_slot, xbc, ctx.n_seqs)
+                             self.scan_floats, ctx.token_seq, ctx.q_start, ctx.seq_slot, xbc, ctx.n_seqs,
+                             single_tokens=ctx.is_decode)
         y = ws.get("mamba2_y", (T, self.inner), torch.float32)
         ops.mamba2_scan(xbc, self.inner, self.inner + self.bc_width, proj[:, self.inner + self.channels:],
                         self.dt_bias, self.a_log, self.d_skip, y, state, 0, ctx.q_start, ctx.seq_slot, ctx.n_seqs,

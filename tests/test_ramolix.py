@@ -385,13 +385,13 @@ def test_the_short_convolution_with_its_state_in_portions_down_to_one_token():
         seqs = [torch.randn(40, ld, generator=g), torch.randn(25, ld, generator=g)]
         before = [torch.zeros(taps - 1, C, dtype=P.DT) for _ in seqs]
         at = [0, 0]
-        for portion in ((1, 2), (1, 1), (2, 1), (3, 17), (30, 1), (3, 3)):
+        for portion in ((1, 2), (1, 1), (1, 1), (2, 1), (3, 17), (30, 1), (1, 1), (1, 1)):
             xs = [s[a:a + n] for s, a, n in zip(seqs, at, portion)]
             proj = torch.cat(xs)
             T = proj.shape[0]
             out = torch.empty(T, C, device="cuda")
             ops.causal_conv_silu(dev(proj), col0, C, dev(w), dev(b), taps, state, off, i32([0] * portion[0] + [1] * portion[1]),
-                                 i32([0, portion[0], T]), i32(slots), out, 2)
+                                 i32([0, portion[0], T]), i32(slots), out, 2, single_tokens=portion == (1, 1))
             want = []
             for i, x in enumerate(xs):
                 y, before[i] = plain_conv(x[:, col0:col0 + C].to(P.DT), w.to(P.DT), b.to(P.DT), before[i])
@@ -709,6 +709,78 @@ def test_long_decoding_from_the_first_token(tmp_path, dtype):
         assert rel_err(torch.cat(got[:6]), ref[:6]) < tol_for(dtype)
         assert model.engine.graph_captures >= 1
         model.check()
+
+
+def random_config(seed):
+    """A configuration drawn from a seed: layer order, every size and every constant."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 64, 96, 128, 136])
+    layers, owners = [], {}
+    for i in range(rng.randint(3, 7)):
+        kind = rng.choice(["attention", "latent_attention", "mamba2"])
+        ff = rng.choice([None, 24, 72, 130])
+        if kind == "attention":
+            kv = rng.choice([1, 2, 3])
+            dim = rng.choice([8, 12, 16, 24, 40, 64])
+            rot = None
+            if rng.random() < 0.8:
+                dims = rng.choice([d for d in (4, 8, 12, 16, 24, 40, 64) if d <= dim])
+                rot = (dims, rng.choice([50.0, 10000.0]))
+                if rng.random() < 0.6:
+                    rot += ((rng.choice([2.0, 8.0]), 1.0, rng.choice([2.0, 4.0, 8.0]), rng.choice([16, 64, 256])),)
+            m = attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.uniform(0.1, 0.4), mask=rng.choice([None, 3, 17, 64, 100, 136]), rot=rot)
+        elif kind == "latent_attention":
+            rank = rng.choice([8, 16, 20, 48, 64])
+            share = [j for j, r in owners.items() if r == rank]
+            kv_from = rng.choice(share) if share and rng.random() < 0.6 else None
+            if kv_from is None:
+                owners[i] = rank
+            m = latent(rng.randint(1, 6), rng.choice([4, 8, 24, 32]), rng.choice([4, 16, 40]), rank, rng.uniform(0.1, 0.5), kv_from)
+        else:
+            groups = rng.choice([1, 2, 3])
+            heads = groups * rng.choice([1, 2])
+            vdim = rng.choice([4, 8, 16, 32])
+            pieces = rng.choice([g for g in (1, 2, 3, 4, 6) if (heads * vdim) % g == 0])
+            m = mamba(heads, vdim, rng.choice([4, 8, 16, 48, 64, 72]), groups, rng.randint(1, 4), pieces)
+        layers.append(layer(kind, m, ff))
+    return config(rng.choice([80, 130, 257]), width, rng.choice([1e-5, 1e-6]), rng.uniform(0.5, 12.0), rng.uniform(0.4, 1.5), layers)
+
+
+def test_random_configurations_are_read_and_written_back():
+    from janus_b200.config import resolve_architecture
+    for seed in range(40):
+        cfg = random_config(seed)
+        arch = resolve_architecture(cfg)
+        c = arch.config_class.from_dict(cfg)
+        assert json.loads(json.dumps(c.to_dict())) == json.loads(json.dumps(cfg)), seed
+        assert {s.name: tuple(s.shape) for s in arch.weight_specs(c)} == {k: tuple(v.shape) for k, v in P.random_weights(cfg, 0).items()}
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_random_configurations_in_prompts_portions_and_single_tokens(tmp_path, seed, dtype):
+    """Layer order, sizes and constants drawn from a seed; two unequal requests in one batch: a prompt each, a
+    portion each, then one token each."""
+    from janus_b200.engine import StepEntry
+    cfg = random_config(seed)
+    d, w = folder(tmp_path, cfg, 40 + seed, sharpen=2.0)
+    model = load(d, dtype, max_tokens=1024, max_slots=4)
+    seqs = [random_tokens(n, cfg["vocab"], seed * 10 + n) for n in (201, 90)]
+    ref = [P.forward(cfg, w, ids) for ids in seqs]
+    slots = [model.alloc_slot() for _ in seqs]
+    rows = Rows(dtype)
+    at = [0, 0]
+    for portion in ((150, 3), (40, 64), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1)):
+        out = model.step([StepEntry(slots[i], seqs[i][at[i]:at[i] + n], range(n)) for i, n in enumerate(portion)]).cpu()
+        row = 0
+        for i, n in enumerate(portion):
+            rows.add(out[row:row + n], ref[i][at[i]:at[i] + n], (seed, i, at[i], n))
+            row += n
+            at[i] += n
+    rows.close()
+    model.check()
 
 
 @gpu
