@@ -11,9 +11,10 @@
 //       y_t = S_t^T C_t + D_h x_t
 //   out = (y * silu(z)) / rms over each of `parts` equal pieces * w
 //
-// mamba2_scan: a block owns one (sequence, head, block of EB value columns); a thread owns two value columns and a
-// quarter of the rows of S in registers, walks the tokens in order (chunks of CT tokens are staged in shared memory,
-// dt and a computed on the way), and the four partial sums of y meet by shuffles in a fixed order.  The state is read
+// mamba2_scan: a block owns one (sequence, head, block of EB value columns); a thread owns four value columns and an
+// eighth of the rows of S in registers, walks the tokens in order (chunks of CT tokens are staged in shared memory,
+// dt and a computed on the way; the decays are applied late, see the kernel), and the eight partial sums of y meet by
+// shuffles in a fixed order.  The state is read
 // from and written back to the sequence's slot, so prompts, portions of prompts and single tokens are the same code.
 //
 // Long prompts run in segments of `seg_len` tokens so that the segments of one sequence run side by side: (1) every
@@ -29,10 +30,11 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int PARTS = 4;      // threads that share a value column (each a quarter of the rows)
-constexpr int EB = 64;        // value columns a block owns, two a thread
+constexpr int PARTS = 8;      // threads that share a value column (each an eighth of the rows)
+constexpr int COLS = 4;       // value columns a thread owns
+constexpr int EB = 64;        // value columns a block owns
 constexpr int CT = 16;        // tokens staged at a time
-constexpr int THREADS = EB / 2 * PARTS;
+constexpr int THREADS = EB / COLS * PARTS;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 // log(1 + exp(z)); beyond 20 the sum is z itself in float32
@@ -99,9 +101,9 @@ __global__ void conv_state_shift_kernel(const float* __restrict__ proj, int ld, 
 // ---- the recurrence -----------------------------------------------------------------------------------------
 enum { WHOLE = 0, LOCAL = 1, FROM_START = 3 };
 
-// RMAX: rows of S a thread holds (a multiple of 4, 4 RMAX >= N); shared rows are padded to 4 RMAX with zeros
+// RMAX: rows of S a thread holds (a multiple of 4, PARTS * RMAX >= N); shared rows are padded to PARTS * RMAX with zeros
 template <int RMAX, int PHASE>
-__global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kernel(
+__global__ void __launch_bounds__(THREADS, RMAX <= 16 ? 4 : 2) mamba2_scan_kernel(
     const float* __restrict__ xbc, int ldx, int b_col, int c_col, const float* __restrict__ dt_raw, int ld_dt,
     const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
     float* __restrict__ out, float* __restrict__ state, long long slot_stride, long long state_off,
@@ -109,22 +111,24 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kerne
     int tiles_per_seq, float* __restrict__ scratch, float* __restrict__ seg_decay) {
   constexpr int phase = PHASE;
   constexpr int DP = PARTS * RMAX;         // padded rows
-  // a part's rows start four floats after the part before ends: the four parts of a column read their 16 bytes
-  // from different banks (with the parts RMAX floats apart, a multiple of 32, all four would meet in one)
+  // a part's rows start four floats after the part before ends: the eight parts of a column read their 16 bytes
+  // from different banks (with the parts RMAX floats apart they would meet in one, two or four banks)
   constexpr int PS = RMAX + 4;             // floats from part to part
   constexpr int TS = PARTS * PS;           // floats from token to token
-  extern __shared__ __align__(16) float smem[];          // B [CT][TS], C [CT][TS], x [CT][EB], dt [CT], a [CT]
+  extern __shared__ __align__(16) float smem[];          // B [CT][TS], C [CT][TS], x [CT][EB], then 3 CT + 1 scalars
   float* b_s = smem;
   float* c_s = b_s + CT * TS;
   float* x_s = c_s + CT * TS;
-  float* dt_s = x_s + CT * EB;
-  float* a_s = dt_s + CT;
+  float* w_s = x_s + CT * EB;              // dt_t / A_t
+  float* A_s = w_s + CT;                   // A_t: the product of the decays since the state was last rescaled
+  float* sc_s = A_s + CT;                  // >= 0: rescale the state by this before token t (its own decay included)
+  float* end_s = sc_s + CT;                // the product that is left when the chunk ends
   jb::pdl_launch_dependents();
   const int seq = blockIdx.x / tiles_per_seq, seg = blockIdx.x % tiles_per_seq;
   const int h = blockIdx.y, e0 = blockIdx.z * EB;
   const int g = h / (H / G);
   const int part = threadIdx.x % PARTS, col = threadIdx.x / PARTS;
-  const int j0 = e0 + 2 * col, j1 = j0 + 1;
+  const int j0 = e0 + COLS * col;
   const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
   jb::pdl_wait();
   const int s0 = q_start[seq], q_len = q_start[seq + 1] - s0;
@@ -136,13 +140,14 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kerne
   float* st = state + (size_t)seq_slot[seq] * slot_stride + state_off + (size_t)h * per_head;     // [N][P]
   float* sc = scratch ? scratch + ((size_t)blockIdx.x * H + h) * per_head : nullptr;
   const float* init = phase == WHOLE ? st : phase == FROM_START ? sc : nullptr;
-  float S0[RMAX], S1[RMAX];
+  float S[COLS][RMAX];
 #pragma unroll
-  for (int i = 0; i < RMAX; ++i) {
-    const int r = part * RMAX + i;
-    S0[i] = (init && r < N && j0 < P) ? init[(size_t)r * P + j0] : 0.0f;
-    S1[i] = (init && r < N && j1 < P) ? init[(size_t)r * P + j1] : 0.0f;
-  }
+  for (int c = 0; c < COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) {
+      const int r = part * RMAX + i;
+      S[c][i] = (init && r < N && j0 + c < P) ? init[(size_t)r * P + j0 + c] : 0.0f;
+    }
   float decay_all = 1.0f;
   for (int c0 = t0; c0 < t1; c0 += CT) {
     const int n = min(CT, t1 - c0);
@@ -159,67 +164,111 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) mamba2_scan_kerne
       const int tt = idx / EB, c = idx % EB;
       x_s[idx] = (tt < n && e0 + c < P) ? xbc[(size_t)(c0 + tt) * ldx + (size_t)h * P + e0 + c] : 0.0f;
     }
-    if (threadIdx.x < n) {
-      const float dt = softplus_f(dt_raw[(size_t)(c0 + threadIdx.x) * ld_dt + h] + bias);
-      dt_s[threadIdx.x] = dt;
-      a_s[threadIdx.x] = expf(neg_a * dt);
+    // The decays are applied late.  With A_t the product of the decays from the last rescaling up to token t, the
+    // registers hold U_t = S_t / A_t, which follows U_t = U_(t-1) + B_t (dt_t x_t / A_t)^T: one FMA an element
+    // instead of a product and an FMA; y_t = A_t U_t^T C_t.  When the product would fall below 2^-40 the registers
+    // are rescaled before that token (its own decay included) and the product starts again at one, so nothing
+    // over- or underflows whatever the step sizes; the chunk's end rescales once more.  Warp 0 computes dt and the
+    // decays, one token a lane, and every lane walks the products in the same order.
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      float dt = 0.0f, a = 1.0f;
+      if (lane < n) {
+        dt = softplus_f(dt_raw[(size_t)(c0 + lane) * ld_dt + h] + bias);
+        a = expf(neg_a * dt);
+      }
+      float run = 1.0f, my_A = 1.0f, my_sc = -1.0f;
+      for (int tt = 0; tt < n; ++tt) {
+        const float at = __shfl_sync(0xffffffffu, a, tt);
+        const float next = run * at;
+        const bool rescale = next < 9.094947e-13f;       // 2^-40
+        run = rescale ? 1.0f : next;
+        if (lane == tt) {
+          my_A = run;
+          my_sc = rescale ? next : -1.0f;
+        }
+        if (phase == LOCAL) decay_all *= at;
+      }
+      if (lane < n) {
+        w_s[lane] = dt / my_A;
+        A_s[lane] = my_A;
+        sc_s[lane] = my_sc;
+      }
+      if (lane == 0) end_s[0] = run;
     }
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
-      const float a = a_s[tt], dt = dt_s[tt];
-      const float2 x = *reinterpret_cast<const float2*>(x_s + tt * EB + 2 * col);
-      const float v0 = dt * x.x, v1 = dt * x.y;
+      const float w = w_s[tt], A = A_s[tt], sc = sc_s[tt];
+      if (sc >= 0.0f) {                                  // the same for every thread of the block
+#pragma unroll
+        for (int c = 0; c < COLS; ++c)
+#pragma unroll
+          for (int i = 0; i < RMAX; ++i) S[c][i] *= sc;
+      }
+      const float4 x = *reinterpret_cast<const float4*>(x_s + tt * EB + COLS * col);
+      const float v[COLS] = {w * x.x, w * x.y, w * x.z, w * x.w};
       const float4* cr = reinterpret_cast<const float4*>(c_s + tt * TS + part * PS);
       const float4* br = reinterpret_cast<const float4*>(b_s + tt * TS + part * PS);
-      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
-      if (phase == LOCAL) decay_all *= a;
+      float acc[COLS][2];
+#pragma unroll
+      for (int c = 0; c < COLS; ++c) acc[c][0] = acc[c][1] = 0.0f;
 #pragma unroll
       for (int i = 0; i < RMAX / 4; ++i) {
         const float4 k4 = br[i];
-        S0[4 * i] = fmaf(a, S0[4 * i], k4.x * v0);
-        S0[4 * i + 1] = fmaf(a, S0[4 * i + 1], k4.y * v0);
-        S0[4 * i + 2] = fmaf(a, S0[4 * i + 2], k4.z * v0);
-        S0[4 * i + 3] = fmaf(a, S0[4 * i + 3], k4.w * v0);
-        S1[4 * i] = fmaf(a, S1[4 * i], k4.x * v1);
-        S1[4 * i + 1] = fmaf(a, S1[4 * i + 1], k4.y * v1);
-        S1[4 * i + 2] = fmaf(a, S1[4 * i + 2], k4.z * v1);
-        S1[4 * i + 3] = fmaf(a, S1[4 * i + 3], k4.w * v1);
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+          S[c][4 * i] = fmaf(k4.x, v[c], S[c][4 * i]);
+          S[c][4 * i + 1] = fmaf(k4.y, v[c], S[c][4 * i + 1]);
+          S[c][4 * i + 2] = fmaf(k4.z, v[c], S[c][4 * i + 2]);
+          S[c][4 * i + 3] = fmaf(k4.w, v[c], S[c][4 * i + 3]);
+        }
         if (phase != LOCAL) {
           const float4 q4 = cr[i];
-          a0 = fmaf(S0[4 * i], q4.x, a0);
-          a1 = fmaf(S0[4 * i + 1], q4.y, a1);
-          a2 = fmaf(S0[4 * i + 2], q4.z, a2);
-          a3 = fmaf(S0[4 * i + 3], q4.w, a3);
-          b0 = fmaf(S1[4 * i], q4.x, b0);
-          b1 = fmaf(S1[4 * i + 1], q4.y, b1);
-          b2 = fmaf(S1[4 * i + 2], q4.z, b2);
-          b3 = fmaf(S1[4 * i + 3], q4.w, b3);
+#pragma unroll
+          for (int c = 0; c < COLS; ++c) {
+            acc[c][0] = fmaf(S[c][4 * i], q4.x, acc[c][0]);
+            acc[c][1] = fmaf(S[c][4 * i + 1], q4.y, acc[c][1]);
+            acc[c][0] = fmaf(S[c][4 * i + 2], q4.z, acc[c][0]);
+            acc[c][1] = fmaf(S[c][4 * i + 3], q4.w, acc[c][1]);
+          }
         }
       }
       if (phase != LOCAL) {
-        float acc0 = (a0 + a1) + (a2 + a3), acc1 = (b0 + b1) + (b2 + b3);
-        // the four parts of a column are neighbouring lanes: part 0 + 1, 2 + 3, then the two sums
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        float y[COLS];
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+          // the eight parts of a column are neighbouring lanes: pairs, then fours, then all eight
+          float t = acc[c][0] + acc[c][1];
+          t += __shfl_xor_sync(0xffffffffu, t, 1);
+          t += __shfl_xor_sync(0xffffffffu, t, 2);
+          t += __shfl_xor_sync(0xffffffffu, t, 4);
+          y[c] = t;
+        }
         if (part == 0) {
           float* orow = out + (size_t)(c0 + tt) * H * P + (size_t)h * P;
-          if (j0 < P) orow[j0] = fmaf(dskip, x.x, acc0);
-          if (j1 < P) orow[j1] = fmaf(dskip, x.y, acc1);
+          const float xs[COLS] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int c = 0; c < COLS; ++c)
+            if (j0 + c < P) orow[j0 + c] = fmaf(dskip, xs[c], A * y[c]);
         }
       }
     }
+    const float left = end_s[0];                         // back to the state itself before the next chunk is staged
+#pragma unroll
+    for (int c = 0; c < COLS; ++c)
+#pragma unroll
+      for (int i = 0; i < RMAX; ++i) S[c][i] *= left;
   }
   if (phase == LOCAL && blockIdx.z == 0 && threadIdx.x == 0) seg_decay[(size_t)blockIdx.x * H + h] = decay_all;
   float* dst = phase == LOCAL ? sc : (last ? st : nullptr);
   if (dst == nullptr) return;
 #pragma unroll
-  for (int i = 0; i < RMAX; ++i) {
-    const int r = part * RMAX + i;
-    if (r < N && j0 < P) dst[(size_t)r * P + j0] = S0[i];
-    if (r < N && j1 < P) dst[(size_t)r * P + j1] = S1[i];
-  }
+  for (int c = 0; c < COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) {
+      const int r = part * RMAX + i;
+      if (r < N && j0 + c < P) dst[(size_t)r * P + j0 + c] = S[c][i];
+    }
 }
 
 // scratch[seq][seg] holds segment seg's state from zero; afterwards it holds the state the segment starts from
@@ -316,8 +365,8 @@ JB_EXPORT int jb_mamba2_scan(const float* xbc, int ldx, int b_col, int c_col, co
   JB_REFUSE(N < 1 || N > 256 || P < 1, "mamba2_scan: state size %d is outside [1, 256]", N);
   JB_REFUSE(G < 1 || H % G != 0, "mamba2_scan: %d heads are not a multiple of %d groups", H, G);
   JB_REFUSE(seg_len > 0 && (scratch == nullptr || seg_decay == nullptr), "mamba2_scan: segments need scratch");
-  const int rmax = N <= 64 ? 16 : N <= 128 ? 32 : 64;
-  const size_t smem = (size_t)(2 * CT * PARTS * (rmax + 4) + CT * EB + 2 * CT) * sizeof(float);
+  const int rmax = N <= 64 ? 8 : N <= 128 ? 16 : 32;
+  const size_t smem = (size_t)(2 * CT * PARTS * (rmax + 4) + CT * EB + 3 * CT + 4) * sizeof(float);
   const bool segmented = seg_len > 0;
   const int tiles = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
   const int seg = segmented ? seg_len : 0x40000000;
@@ -331,9 +380,9 @@ JB_EXPORT int jb_mamba2_scan(const float* xbc, int ldx, int b_col, int c_col, co
   } while (0)
 #define JB_LAUNCH_MS_R(PHASE)                       \
   do {                                              \
-    if (rmax == 16) JB_LAUNCH_MS(16, PHASE);        \
-    else if (rmax == 32) JB_LAUNCH_MS(32, PHASE);   \
-    else JB_LAUNCH_MS(64, PHASE);                   \
+    if (rmax == 8) JB_LAUNCH_MS(8, PHASE);          \
+    else if (rmax == 16) JB_LAUNCH_MS(16, PHASE);   \
+    else JB_LAUNCH_MS(32, PHASE);                   \
   } while (0)
   if (!segmented) {
     JB_LAUNCH_MS_R(WHOLE);

@@ -469,18 +469,22 @@ def test_the_recurrence_whole_in_segments_and_token_by_token():
         for _ in range(3):                               # one token each, from the state that was left
             xbc, dt_raw = torch.randn(3, ld, generator=g), torch.randn(3, H, generator=g)
             assert rel_err(run(xbc, dt_raw, (1, 1, 1), True), plain(xbc, dt_raw, (1, 1, 1))) < 2e-5
-    # a large step size and a strongly negative one: softplus has no clamp
+    # large step sizes and strongly negative ones (softplus has no clamp), with decays from next to one down to
+    # nothing at all: the late decays are rescaled in time, nothing over- or underflows
     H, G, N, Pv = 2, 1, 4, 4
-    state = torch.zeros(1, H * N * Pv, device="cuda")
-    xbc, dt_raw = torch.randn(6, H * Pv + 2 * G * N, generator=g), torch.tensor([[30.0, -30.0]] * 6)
-    zeros = torch.zeros(H)
-    out = torch.empty(6, H * Pv, device="cuda")
-    ops.mamba2_scan(dev(xbc), H * Pv, H * Pv + G * N, dev(dt_raw), dev(zeros), dev(zeros - 3.0), dev(zeros), out, state, 0,
-                    i32([0, 6]), i32([0]), 1, H, G, N, Pv, 6, None)
-    seg = xbc.to(P.DT)
-    y, _ = plain_scan(seg[:, :H * Pv].reshape(6, H, Pv), seg[:, H * Pv:H * Pv + N].reshape(6, G, N), seg[:, H * Pv + N:].reshape(6, G, N),
-                      dt_raw.to(P.DT), zeros.to(P.DT), zeros.to(P.DT) - 3.0, zeros.to(P.DT), torch.zeros(H, N, Pv, dtype=P.DT))
-    assert rel_err(out.cpu(), y.reshape(6, H * Pv)) < 2e-5
+    for a_log, T in ((-3.0, 6), (3.0, 40), (0.5, 300), (-8.0, 300)):
+        state = torch.zeros(1, H * N * Pv, device="cuda")
+        xbc = torch.randn(T, H * Pv + 2 * G * N, generator=g)
+        dt_raw = torch.tensor([[30.0, -30.0], [2.0, 0.0], [-1.0, 8.0]] * ((T + 2) // 3))[:T]
+        zeros = torch.zeros(H)
+        out = torch.empty(T, H * Pv, device="cuda")
+        ops.mamba2_scan(dev(xbc), H * Pv, H * Pv + G * N, dev(dt_raw), dev(zeros), dev(zeros + a_log), dev(zeros), out, state, 0,
+                        i32([0, T]), i32([0]), 1, H, G, N, Pv, T, None)
+        seg = xbc.to(P.DT)
+        y, S = plain_scan(seg[:, :H * Pv].reshape(T, H, Pv), seg[:, H * Pv:H * Pv + N].reshape(T, G, N), seg[:, H * Pv + N:].reshape(T, G, N),
+                          dt_raw.to(P.DT), zeros.to(P.DT), zeros.to(P.DT) + a_log, zeros.to(P.DT), torch.zeros(H, N, Pv, dtype=P.DT))
+        assert rel_err(out.cpu(), y.reshape(T, H * Pv)) < 2e-5, a_log
+        assert rel_err(state.cpu().view(H, N, Pv), S) < 2e-5, a_log
 
 
 @gpu
