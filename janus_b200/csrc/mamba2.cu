@@ -152,17 +152,40 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 16 ? 4 : 2) mamba2_scan_kerne
   for (int c0 = t0; c0 < t1; c0 += CT) {
     const int n = min(CT, t1 - c0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * DP; idx += THREADS) {
-      const int tt = idx / DP, r = idx % DP;
-      const bool in = r < N;
-      const float* row = xbc + (size_t)(c0 + tt) * ldx + (size_t)g * N + (in ? r : 0);
-      const int at = tt * TS + (r / RMAX) * PS + r % RMAX;
-      b_s[at] = in ? row[b_col] : 0.0f;
-      if (phase != LOCAL) c_s[at] = in ? row[c_col] : 0.0f;
+    // eight loads of each kind are in flight before the first is stored (a load a time would leave the block
+    // waiting on memory for most of a chunk)
+    for (int base = 0; base < n * DP; base += 8 * THREADS) {
+      float bv[8], cv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * THREADS + threadIdx.x;
+        const int tt = idx / DP, r = idx % DP;
+        const bool in = idx < n * DP && r < N;
+        const float* row = xbc + (size_t)(c0 + (in ? tt : 0)) * ldx + (size_t)g * N + (in ? r : 0);
+        bv[u] = in ? row[b_col] : 0.0f;
+        cv[u] = (in && phase != LOCAL) ? row[c_col] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * THREADS + threadIdx.x;
+        if (idx < n * DP) {
+          const int tt = idx / DP, r = idx % DP;
+          const int at = tt * TS + (r / RMAX) * PS + r % RMAX;
+          b_s[at] = bv[u];
+          if (phase != LOCAL) c_s[at] = cv[u];
+        }
+      }
     }
-    for (int idx = threadIdx.x; idx < CT * EB; idx += THREADS) {
-      const int tt = idx / EB, c = idx % EB;
-      x_s[idx] = (tt < n && e0 + c < P) ? xbc[(size_t)(c0 + tt) * ldx + (size_t)h * P + e0 + c] : 0.0f;
+    {
+      float xv[CT * EB / THREADS];
+#pragma unroll
+      for (int u = 0; u < CT * EB / THREADS; ++u) {
+        const int idx = u * THREADS + threadIdx.x;
+        const int tt = idx / EB, c = idx % EB;
+        xv[u] = (tt < n && e0 + c < P) ? xbc[(size_t)(c0 + tt) * ldx + (size_t)h * P + e0 + c] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < CT * EB / THREADS; ++u) x_s[u * THREADS + threadIdx.x] = xv[u];
     }
     // The decays are applied late.  With A_t the product of the decays from the last rescaling up to token t, the
     // registers hold U_t = S_t / A_t, which follows U_t = U_(t-1) + B_t (dt_t x_t / A_t)^T: one FMA an element
@@ -288,12 +311,23 @@ __global__ void mamba2_prefix_kernel(float* __restrict__ scratch, const float* _
   float S = state[(size_t)seq_slot[seq] * slot_stride + state_off + idx];
   float* p = scratch + (size_t)seq * tiles_per_seq * per + idx;
   const float* dec = seg_decay + (size_t)seq * tiles_per_seq * H + h;
-  for (int seg = 0; seg < n_seg; ++seg) {
-    const bool has_local = seg + 1 < n_seg;          // the last segment left nothing
-    const float local = has_local ? p[(size_t)seg * per] : 0.0f;
-    const float d = has_local ? dec[(size_t)seg * H] : 0.0f;
-    p[(size_t)seg * per] = S;
-    S = fmaf(d, S, local);
+  // eight segments' states from zero and decays are on their way before the first is used (one at a time, every
+  // segment would wait for its own load behind the store of the segment before)
+  for (int seg0 = 0; seg0 < n_seg; seg0 += 8) {
+    float local[8], d[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const bool has_local = seg0 + u + 1 < n_seg;   // the last segment left nothing
+      local[u] = has_local ? p[(size_t)(seg0 + u) * per] : 0.0f;
+      d[u] = has_local ? dec[(size_t)(seg0 + u) * H] : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (seg0 + u < n_seg) {
+        p[(size_t)(seg0 + u) * per] = S;
+        S = fmaf(d[u], S, local[u]);
+      }
+    }
   }
 }
 
