@@ -31,7 +31,7 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 constexpr int PARTS = 8;      // threads that share a value column (each an eighth of the rows)
-constexpr int COLS = 4;       // value columns a thread owns
+constexpr int COLS = 4;       // value columns a thread owns (the 16-byte state accesses below are written for four)
 constexpr int EB = 64;        // value columns a block owns
 constexpr int CT = 16;        // tokens staged at a time
 constexpr int THREADS = EB / COLS * PARTS;
@@ -141,13 +141,28 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 16 ? 4 : 2) mamba2_scan_kerne
   float* sc = scratch ? scratch + ((size_t)blockIdx.x * H + h) * per_head : nullptr;
   const float* init = phase == WHOLE ? st : phase == FROM_START ? sc : nullptr;
   float S[COLS][RMAX];
-#pragma unroll
-  for (int c = 0; c < COLS; ++c)
+  // a thread's four columns of a row are 16 bytes of the state: one load where the rows are aligned
+  const bool vec_in = init != nullptr && (P & 3) == 0 && ((uintptr_t)init & 15) == 0;
+  if (vec_in) {
 #pragma unroll
     for (int i = 0; i < RMAX; ++i) {
       const int r = part * RMAX + i;
-      S[c][i] = (init && r < N && j0 + c < P) ? init[(size_t)r * P + j0 + c] : 0.0f;
+      float4 v4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (r < N && j0 < P) v4 = *reinterpret_cast<const float4*>(init + (size_t)r * P + j0);
+      S[0][i] = v4.x;
+      S[1][i] = v4.y;
+      S[2][i] = v4.z;
+      S[3][i] = v4.w;
     }
+  } else {
+#pragma unroll
+    for (int c = 0; c < COLS; ++c)
+#pragma unroll
+      for (int i = 0; i < RMAX; ++i) {
+        const int r = part * RMAX + i;
+        S[c][i] = (init && r < N && j0 + c < P) ? init[(size_t)r * P + j0 + c] : 0.0f;
+      }
+  }
   float decay_all = 1.0f;
   for (int c0 = t0; c0 < t1; c0 += CT) {
     const int n = min(CT, t1 - c0);
@@ -285,6 +300,15 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 16 ? 4 : 2) mamba2_scan_kerne
   if (phase == LOCAL && blockIdx.z == 0 && threadIdx.x == 0) seg_decay[(size_t)blockIdx.x * H + h] = decay_all;
   float* dst = phase == LOCAL ? sc : (last ? st : nullptr);
   if (dst == nullptr) return;
+  if ((P & 3) == 0 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) {
+      const int r = part * RMAX + i;
+      if (r < N && j0 < P)
+        *reinterpret_cast<float4*>(dst + (size_t)r * P + j0) = make_float4(S[0][i], S[1][i], S[2][i], S[3][i]);
+    }
+    return;
+  }
 #pragma unroll
   for (int c = 0; c < COLS; ++c)
 #pragma unroll
