@@ -450,6 +450,57 @@ __global__ void sublayer_norm_add_kernel(float* __restrict__ y, const TG* __rest
     if (x_out != nullptr) x_out[row + i] = jb::from_f32<TO>(r);
   }
 }
+// Rows whose width is a multiple of 4: 16-byte accesses, the row of y stays in registers between the two passes
+// (CACHE float4 a thread cover rows of 4 * CACHE * THREADS floats; wider rows are read twice).
+template <typename TG, typename TO, int THREADS, int CACHE>
+__global__ void __launch_bounds__(THREADS) sublayer_norm_add_vec_kernel(float* __restrict__ y, const TG* __restrict__ gamma,
+                                                                         float eps, float mult, float* __restrict__ residual,
+                                                                         TO* __restrict__ x_out, int H,
+                                                                         float4* __restrict__ clear, size_t clear_n4) {
+  __shared__ float scratch[THREADS / 32];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  clear_slice(clear, clear_n4);
+  const size_t row = (size_t)blockIdx.x * H;
+  float* res = residual + row;
+  const int n4 = H >> 2;
+  if (y == nullptr) {
+    for (int i = threadIdx.x; i < n4; i += THREADS) store4(x_out + row + 4 * i, load4(res + 4 * i));
+    return;
+  }
+  float* yr = y + row;
+  float4 cache[CACHE];
+  float ss = 0.0f;
+#pragma unroll
+  for (int c = 0; c < CACHE; ++c) {
+    const int i = threadIdx.x + c * THREADS;
+    if (i < n4) {
+      cache[c] = load4(yr + 4 * i);
+      ss += cache[c].x * cache[c].x + cache[c].y * cache[c].y + cache[c].z * cache[c].z + cache[c].w * cache[c].w;
+    }
+  }
+  for (int i = threadIdx.x + CACHE * THREADS; i < n4; i += THREADS) {
+    const float4 v = load4(yr + 4 * i);
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = norm_block_sum<THREADS>(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  auto finish = [&](int i, float4 v) {
+    const float4 g = load4(gamma + 4 * i), r = load4(res + 4 * i);
+    const float4 o = make_float4(r.x + mult * ((v.x / rms) * g.x), r.y + mult * ((v.y / rms) * g.y),
+                                 r.z + mult * ((v.z / rms) * g.z), r.w + mult * ((v.w / rms) * g.w));
+    store4(res + 4 * i, o);
+    store4(yr + 4 * i, zero);
+    if (x_out != nullptr) store4(x_out + row + 4 * i, o);
+  };
+#pragma unroll
+  for (int c = 0; c < CACHE; ++c) {
+    const int i = threadIdx.x + c * THREADS;
+    if (i < n4) finish(i, cache[c]);
+  }
+  for (int i = threadIdx.x + CACHE * THREADS; i < n4; i += THREADS) finish(i, load4(yr + 4 * i));
+}
 }  // namespace
 
 JB_EXPORT int jb_sublayer_norm_add(float* y, const void* gamma, int gamma_dtype, float eps, float mult, float* residual,
@@ -461,11 +512,16 @@ JB_EXPORT int jb_sublayer_norm_add(float* y, const void* gamma, int gamma_dtype,
   JB_REFUSE(y == nullptr && x_out == nullptr, "sublayer_norm_add: nothing to do");
   float4* clear4 = (float4*)clear;
   const size_t clear_n4 = clear ? (size_t)clear_n >> 2 : 0;
-  jb::Launch cfg(dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream);
+  const bool vec = (H & 3) == 0, narrow = H <= 2048;
+  jb::Launch cfg(dim3(T), dim3(vec ? (narrow ? 128 : 256) : (H >= 1024 ? 256 : 128)), 0, stream);
   cudaError_t e;
-#define JB_LAUNCH_SN(TG, TO)                                                                                      \
-  e = cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_kernel<TG, TO>, y, (const TG*)gamma, eps, mult, residual,     \
-                         (TO*)x_out, H, clear4, clear_n4)
+#define JB_LAUNCH_SN(TG, TO)                                                                                        \
+  e = !vec     ? cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_kernel<TG, TO>, y, (const TG*)gamma, eps, mult,      \
+                                    residual, (TO*)x_out, H, clear4, clear_n4)                                     \
+      : narrow ? cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_vec_kernel<TG, TO, 128, 4>, y, (const TG*)gamma, eps, \
+                                    mult, residual, (TO*)x_out, H, clear4, clear_n4)                               \
+               : cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_vec_kernel<TG, TO, 256, 8>, y, (const TG*)gamma, eps, \
+                                    mult, residual, (TO*)x_out, H, clear4, clear_n4)
   if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_SN(float, float);
   else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_SN(float, bf16);
   else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_SN(bf16, float);

@@ -79,6 +79,79 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ proj, int ld, 
   out[(size_t)t * C + c] = silu_f(acc);
 }
 
+// Prompt steps whose rows are whole 16-byte vectors: a thread owns four channels and walks CONV_TOKENS tokens in a
+// row, keeping the last taps - 1 inputs in registers, so an input is read once instead of `taps` times; where a
+// sequence begins inside the tile (or the tile begins) the window is filled anew from the tokens before or the state.
+constexpr int CONV_TOKENS = 16;
+constexpr int CONV_MAX_TAPS = 8;
+
+__device__ __forceinline__ float4 silu4(float4 v) {
+  return make_float4(silu_f(v.x), silu_f(v.y), silu_f(v.z), silu_f(v.w));
+}
+
+__global__ void causal_conv_silu_vec_kernel(const float* __restrict__ proj, int ld, int col0, int C,
+                                            const float* __restrict__ w, const float* __restrict__ bias, int taps,
+                                            const float* __restrict__ state, long long slot_stride, long long state_off,
+                                            const int* __restrict__ token_seq, const int* __restrict__ q_start,
+                                            const int* __restrict__ seq_slot, float* __restrict__ out, int T) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= C) return;
+  float wr[4][CONV_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) wr[k][j] = j < taps ? w[(size_t)(c + k) * taps + j] : 0.0f;
+  const float4 b4 = bias != nullptr ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float4 win[CONV_MAX_TAPS - 1];          // win[j]: the input taps - 1 - j tokens back (slots taps - 1 and up unused)
+  const int t0 = blockIdx.x * CONV_TOKENS, t1 = min(T, t0 + CONV_TOKENS);
+  int seq_before = -1;
+  for (int t = t0; t < t1; ++t) {
+    const int seq = token_seq[t];
+    if (seq != seq_before) {               // the tile's first token, or a sequence's first: fill the window
+      const int s0 = q_start[seq], li = t - s0;
+      const float* st = state + (size_t)seq_slot[seq] * slot_stride + state_off;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+        if (j < taps - 1) {
+          const int src = li - (taps - 1) + j;
+          win[j] = src >= 0 ? *reinterpret_cast<const float4*>(proj + (size_t)(s0 + src) * ld + col0 + c)
+                            : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + src) * C + c);
+        }
+      }
+      seq_before = seq;
+    }
+    const float4 u = *reinterpret_cast<const float4*>(proj + (size_t)t * ld + col0 + c);
+    float4 acc = b4;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+      if (j < taps - 1) {
+        acc.x = fmaf(wr[0][j], win[j].x, acc.x);
+        acc.y = fmaf(wr[1][j], win[j].y, acc.y);
+        acc.z = fmaf(wr[2][j], win[j].z, acc.z);
+        acc.w = fmaf(wr[3][j], win[j].w, acc.w);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+      if (j == taps - 1) {
+        acc.x = fmaf(wr[0][j], u.x, acc.x);
+        acc.y = fmaf(wr[1][j], u.y, acc.y);
+        acc.z = fmaf(wr[2][j], u.z, acc.z);
+        acc.w = fmaf(wr[3][j], u.w, acc.w);
+      }
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * C + c) = silu4(acc);
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 2; ++j)
+      if (j < taps - 2) win[j] = win[j + 1];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+      if (j == taps - 2) win[j] = u;
+  }
+}
+
 // After a step: the state becomes the last taps - 1 inputs of each sequence (older ones move up when the step
 // brought fewer tokens than that).  One thread per (sequence, channel) walks the rows in order, so a row is read
 // before it is written.
@@ -390,10 +463,17 @@ JB_EXPORT int jb_causal_conv_silu(const float* proj, int ld, int col0, int C, co
   if (T <= 0) return 0;
   JB_REFUSE(taps < 1 || ld < col0 + C, "causal_conv_silu: %d taps over columns %d..%d of %d", taps, col0, col0 + C, ld);
   JB_REFUSE(taps > 1 && state == nullptr, "causal_conv_silu: a convolution of %d taps needs its state", taps);
-  {
-    jb::Launch cfg(dim3(T, (C + 127) / 128), dim3(128), 0, stream);
-    JB_REFUSE(single_tokens && T != n_seqs, "causal_conv_silu: %d tokens are not one for each of %d sequences", T, n_seqs);
+  JB_REFUSE(single_tokens && T != n_seqs, "causal_conv_silu: %d tokens are not one for each of %d sequences", T, n_seqs);
+  const bool aligned = ((C | ld | col0) & 3) == 0 && ((slot_stride | state_off) & 3) == 0 &&
+                       (((uintptr_t)proj | (uintptr_t)out | (uintptr_t)state | (uintptr_t)bias) & 15) == 0;
+  if (!single_tokens && aligned && taps <= CONV_MAX_TAPS && T >= 4 * CONV_TOKENS) {
+    jb::Launch cfg(dim3((T + CONV_TOKENS - 1) / CONV_TOKENS, (C / 4 + 127) / 128), dim3(128), 0, stream);
+    cudaError_t e = cudaLaunchKernelEx(&cfg.c, causal_conv_silu_vec_kernel, proj, ld, col0, C, w, bias, taps,
+                                       (const float*)state, slot_stride, state_off, token_seq, q_start, seq_slot, out, T);
+    if (e != cudaSuccess) return (int)e;
+  } else {
     const int shift_here = (update_state && single_tokens) ? 1 : 0;
+    jb::Launch cfg(dim3(T, (C + 127) / 128), dim3(128), 0, stream);
     cudaError_t e = cudaLaunchKernelEx(&cfg.c, causal_conv_silu_kernel, proj, ld, col0, C, w, bias, taps,
                                        (const float*)state, slot_stride, state_off, token_seq, q_start, seq_slot, out,
                                        shift_here);

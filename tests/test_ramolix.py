@@ -251,7 +251,7 @@ def i32(values):
 def test_output_norm_sum_and_the_gelu_gate_against_their_formulas():
     from janus_b200.kernels import ops
     g = torch.Generator().manual_seed(0)
-    for T, H, mult in ((7, 40, 0.6), (3, 33, 1.0), (5, 2048, 1.7)):
+    for T, H, mult in ((7, 40, 0.6), (3, 33, 1.0), (5, 2048, 1.7), (2, 4100, 0.5), (2, 8200, 1.1)):
         res, y, gamma = torch.randn(T, H, generator=g), torch.randn(T, H, generator=g) * 3, torch.randn(H, generator=g)
         want = res.to(P.DT) + mult * P.rms_norm(y.to(P.DT), gamma.to(P.DT), 1e-5)
         for out_dtype in (torch.float32, torch.bfloat16):
@@ -377,15 +377,16 @@ def plain_conv(u, w, b, before):
 def test_the_short_convolution_with_its_state_in_portions_down_to_one_token():
     from janus_b200.kernels import ops
     g = torch.Generator().manual_seed(4)
-    for C, taps in ((20, 4), (7, 2), (130, 1), (33, 5)):
-        col0, ld, off = 3, C + 8, 11
+    for C, taps, col0, pad, off in ((20, 4, 3, 8, 11), (7, 2, 3, 8, 11), (130, 1, 3, 8, 11), (33, 5, 3, 8, 11),
+                                    (24, 4, 4, 8, 12), (520, 3, 8, 4, 0), (16, 8, 0, 0, 4), (12, 1, 4, 4, 8)):
+        ld = col0 + C + pad       # the last four: whole 16-byte vectors everywhere, prompt steps take the vector kernel
         w, b = torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
-        state = torch.zeros(4, off + (taps - 1) * C + 2, device="cuda")
+        state = torch.zeros(4, off + (taps - 1) * C + (2 if pad == 8 else 4), device="cuda")
         slots = [2, 0]
-        seqs = [torch.randn(40, ld, generator=g), torch.randn(25, ld, generator=g)]
+        seqs = [torch.randn(140, ld, generator=g), torch.randn(125, ld, generator=g)]
         before = [torch.zeros(taps - 1, C, dtype=P.DT) for _ in seqs]
         at = [0, 0]
-        for portion in ((1, 2), (1, 1), (1, 1), (2, 1), (3, 17), (30, 1), (1, 1), (1, 1)):
+        for portion in ((1, 2), (1, 1), (1, 1), (2, 1), (3, 17), (30, 1), (1, 1), (1, 1), (33, 70), (2, 29), (65, 1)):
             xs = [s[a:a + n] for s, a, n in zip(seqs, at, portion)]
             proj = torch.cat(xs)
             T = proj.shape[0]
