@@ -451,6 +451,47 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const fl
     out[(size_t)t * N + c0 + i] = jb::from_f32<TO>(((row[i] * silu_f(g[i])) / rms) * w[c0 + i]);
 }
 
+__device__ __forceinline__ void store4_out(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4_out(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// Pieces made of whole 16-byte vectors: the gated values stay in shared memory between the two passes (the piece is
+// read once), 16 bytes a thread.
+template <typename TO>
+__global__ void gated_group_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ gate, int gate_ld,
+                                               const float* __restrict__ w, float eps, TO* __restrict__ out, int N,
+                                               int parts) {
+  extern __shared__ __align__(16) float gated_s[];       // the piece's gated values
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x, piece = blockIdx.y;
+  const int n = N / parts, c0 = piece * n, n4 = n >> 2;
+  const float4* row = reinterpret_cast<const float4*>(y + (size_t)t * N + c0);
+  const float4* g = reinterpret_cast<const float4*>(gate + (size_t)t * gate_ld + c0);
+  float4* gs = reinterpret_cast<float4*>(gated_s);
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 a = row[i], z = g[i];
+    const float4 v = make_float4(a.x * silu_f(z.x), a.y * silu_f(z.y), a.z * silu_f(z.z), a.w * silu_f(z.w));
+    gs[i] = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = jb::block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)n + eps);
+  const float4* w4 = reinterpret_cast<const float4*>(w + c0);
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {     // a thread reads back what it wrote itself
+    const float4 v = gs[i], ww = w4[i];
+    store4_out(out + (size_t)t * N + c0 + 4 * i,
+               make_float4((v.x / rms) * ww.x, (v.y / rms) * ww.y, (v.z / rms) * ww.z, (v.w / rms) * ww.w));
+  }
+}
+
 }  // namespace
 
 // out[t, c] = silu(bias[c] + sum_j w[c][j] u[t - taps + 1 + j][c]) over the columns [col0, col0 + C) of proj.
@@ -547,7 +588,20 @@ JB_EXPORT int jb_gated_group_rmsnorm(const float* y, const float* gate, int gate
                                      void* out, int out_dtype, int T, int N, int parts, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(parts < 1 || N % parts != 0, "gated_group_rmsnorm: %d numbers do not fall into %d equal pieces", N, parts);
-  jb::Launch cfg(dim3(T, parts), dim3(N / parts >= 2048 ? 256 : 128), 0, stream);
+  const int n = N / parts;
+  const bool aligned = ((n | N | gate_ld) & 3) == 0 && n * (int)sizeof(float) <= 48 * 1024 &&
+                       (((uintptr_t)y | (uintptr_t)gate | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+  if (aligned) {
+    jb::Launch cfg(dim3(T, parts), dim3(n >= 2048 ? 256 : 128), (size_t)n * sizeof(float), stream);
+    if (out_dtype == JB_F32)
+      return (int)cudaLaunchKernelEx(&cfg.c, gated_group_rmsnorm_vec_kernel<float>, y, gate, gate_ld, w, eps, (float*)out,
+                                     N, parts);
+    if (out_dtype == JB_BF16)
+      return (int)cudaLaunchKernelEx(&cfg.c, gated_group_rmsnorm_vec_kernel<bf16>, y, gate, gate_ld, w, eps, (bf16*)out,
+                                     N, parts);
+    return JB_ERR_BAD_DTYPE;
+  }
+  jb::Launch cfg(dim3(T, parts), dim3(n >= 2048 ? 256 : 128), 0, stream);
   if (out_dtype == JB_F32)
     return (int)cudaLaunchKernelEx(&cfg.c, gated_group_rmsnorm_kernel<float>, y, gate, gate_ld, w, eps, (float*)out, N,
                                    parts);

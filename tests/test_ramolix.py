@@ -492,15 +492,15 @@ def test_the_recurrence_whole_in_segments_and_token_by_token():
 def test_the_gate_comes_before_the_norm_and_pieces_are_normed_apart():
     from janus_b200.kernels import ops
     g = torch.Generator().manual_seed(6)
-    for N, parts in ((48, 2), (30, 3), (64, 1), (4096, 2)):
-        T = 5
-        y, gate, w = torch.randn(T, N, generator=g) * 2, torch.randn(T, N + 6, generator=g), torch.randn(N, generator=g)
-        gated = y.to(P.DT) * P.silu(gate[:, 2:2 + N].to(P.DT))
+    for N, parts, lead in ((48, 2, 2), (30, 3, 2), (64, 1, 2), (4096, 2, 2), (48, 2, 4), (4096, 1, 8), (120, 5, 0)):
+        T = 5         # lead 2: the gate's rows start off a 16-byte boundary (scalar kernel); else whole vectors
+        y, gate, w = torch.randn(T, N, generator=g) * 2, torch.randn(T, N + 8, generator=g), torch.randn(N, generator=g)
+        gated = y.to(P.DT) * P.silu(gate[:, lead:lead + N].to(P.DT))
         want = P.rms_unit(gated.reshape(T, parts, N // parts), 1e-5).reshape(T, N) * w.to(P.DT)
         gd = dev(gate)
         for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2)):
             out = torch.empty(T, N, dtype=dtype, device="cuda")
-            ops.gated_group_rmsnorm(dev(y), gd[:, 2:2 + N], dev(w), 1e-5, parts, out)
+            ops.gated_group_rmsnorm(dev(y), gd[:, lead:lead + N], dev(w), 1e-5, parts, out)
             assert rel_err(out.float().cpu(), want) < tol
         if parts > 1:       # one norm over the whole row is another result
             assert rel_err(P.rms_unit(gated, 1e-5) * w.to(P.DT), want) > 1e-2
