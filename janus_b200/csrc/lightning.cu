@@ -45,10 +45,14 @@ __global__ void __launch_bounds__(EB / 2 * PARTS, RMAX <= 32 ? 4 : 2) lightning_
     const float* __restrict__ decay, int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch) {
   constexpr int phase = PHASE;             // the pass from zero needs neither queries nor outputs
   constexpr int DP = PARTS * RMAX;         // padded rows
-  extern __shared__ __align__(16) float smem[];          // q [CT][DP], k [CT][DP], v [CT][EB]
+  // a part's rows start four floats after the part before ends: the four parts of a column read their 16 bytes
+  // from different banks (with the parts RMAX floats apart, a multiple of 16, they would meet in one or two)
+  constexpr int PS = RMAX + 4;             // floats from part to part
+  constexpr int TS = PARTS * PS;           // floats from token to token
+  extern __shared__ __align__(16) float smem[];          // q [CT][TS], k [CT][TS], v [CT][EB]
   float* q_s = smem;
-  float* k_s = q_s + CT * DP;
-  float* v_s = k_s + CT * DP;
+  float* k_s = q_s + CT * TS;
+  float* v_s = k_s + CT * TS;
   jb::pdl_launch_dependents();
   const int seq = blockIdx.x / tiles_per_seq, seg = blockIdx.x % tiles_per_seq;
   const int h = blockIdx.y, e0 = blockIdx.z * EB;
@@ -91,9 +95,11 @@ __global__ void __launch_bounds__(EB / 2 * PARTS, RMAX <= 32 ? 4 : 2) lightning_
       for (int u = 0; u < 8; ++u) {
         const int idx = base + u * THREADS + threadIdx.x;
         if (idx < n * DP) {
-          const bool in = idx % DP < d;
-          if (phase != LOCAL) q_s[idx] = in ? silu_f(qv[u]) : 0.0f;
-          k_s[idx] = in ? silu_f(kv[u]) : 0.0f;
+          const int r = idx % DP;
+          const bool in = r < d;
+          const int at = (idx / DP) * TS + (r / RMAX) * PS + r % RMAX;
+          if (phase != LOCAL) q_s[at] = in ? silu_f(qv[u]) : 0.0f;
+          k_s[at] = in ? silu_f(kv[u]) : 0.0f;
         }
       }
     }
@@ -116,8 +122,8 @@ __global__ void __launch_bounds__(EB / 2 * PARTS, RMAX <= 32 ? 4 : 2) lightning_
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float2 v = *reinterpret_cast<const float2*>(v_s + tt * EB + 2 * col);
-      const float4* qr = reinterpret_cast<const float4*>(q_s + tt * DP + part * RMAX);
-      const float4* kr = reinterpret_cast<const float4*>(k_s + tt * DP + part * RMAX);
+      const float4* qr = reinterpret_cast<const float4*>(q_s + tt * TS + part * PS);
+      const float4* kr = reinterpret_cast<const float4*>(k_s + tt * TS + part * PS);
       float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
 #pragma unroll
       for (int i = 0; i < RMAX / 4; ++i) {
@@ -233,7 +239,7 @@ JB_EXPORT int jb_lightning_scan(const float* proj, int ld, int q_col, int k_col,
   JB_REFUSE(d < 1 || d > 256 || e < 1, "lightning_scan: key size %d is outside [1, 256]", d);
   JB_REFUSE(seg_len > 0 && scratch == nullptr, "lightning_scan: segments need scratch");
   const int rmax = d <= 64 ? 16 : d <= 128 ? 32 : 64;
-  const size_t smem = (size_t)(2 * CT * PARTS * rmax + CT * EB) * sizeof(float);
+  const size_t smem = (size_t)(2 * CT * PARTS * (rmax + 4) + CT * EB) * sizeof(float);
   const bool segmented = seg_len > 0;
   const int tiles = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
   const int seg = segmented ? seg_len : 0x40000000;
