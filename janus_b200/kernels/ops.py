@@ -1238,6 +1238,28 @@ def latent_prep(proj: torch.Tensor, q_width: int, rank: int, weight: Optional[to
 MAMBA2_SEGMENT = 128     # tokens of a segment when a long prompt's recurrence runs in segments side by side
 
 
+@functools.lru_cache(maxsize=None)
+def _sm_count() -> int:
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+def mamba2_segment_for(n_seqs: int, max_q_len: int, heads: int, n_state: int, vdim: int) -> int:
+    """Tokens a segment when the recurrence of a long prompt runs in segments: a block walks one (segment, head, 64
+    value columns), four blocks share an SM (two for more than 128 state rows), and the blocks run in waves; the
+    length (a multiple of the 16 tokens staged at a time, 64 to 256) is the one whose waves x length is least,
+    with a little for every further segment (the prefix pass walks them one after another).  2,048 tokens of 64
+    heads on 148 SMs: 128 tokens make 1,024 blocks, two waves of the 592 that fit; 240 tokens make 576, one wave."""
+    slots = _sm_count() * (4 if n_state <= 128 else 2)
+    best, best_cost = MAMBA2_SEGMENT, None
+    for seg in range(64, 257, 16):
+        tiles = (max_q_len + seg - 1) // seg
+        blocks = n_seqs * tiles * heads * ((vdim + 63) // 64)
+        cost = ((blocks + slots - 1) // slots) * seg + 2 * tiles
+        if best_cost is None or cost < best_cost:
+            best, best_cost = seg, cost
+    return best
+
+
 def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      taps: int, state: Optional[torch.Tensor], state_off: int, token_seq: torch.Tensor,
                      q_start: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, n_seqs: int,
@@ -1296,7 +1318,7 @@ def mamba2_scan(xbc: torch.Tensor, b_col: int, c_col: int, dt_raw: torch.Tensor,
         raise KernelError("mamba2_scan: the columns reach past the rows")
     seg, scratch, seg_decay = 0, None, None
     if workspace is not None and max_q_len > 2 * MAMBA2_SEGMENT:
-        seg = MAMBA2_SEGMENT
+        seg = mamba2_segment_for(n_seqs, max_q_len, heads, n_state, vdim)
         tiles = (max_q_len + seg - 1) // seg
         scratch = workspace.get("mamba2_segments", (n_seqs * tiles * heads * n_state * vdim,), torch.float32)
         seg_decay = workspace.get("mamba2_segment_decay", (n_seqs * tiles * heads,), torch.float32)
