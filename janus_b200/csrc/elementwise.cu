@@ -36,7 +36,7 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 template <typename TT>
 __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, const int* __restrict__ feedback,
-                                    const int* __restrict__ token_slot) {
+                                    const int* __restrict__ token_slot, float scale) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x;
@@ -45,9 +45,12 @@ __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __r
   const TT* row = table + (size_t)id * H;
   float* o = out + (size_t)t * H;
   if ((H & 3) == 0) {
-    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) store4(o + i, load4(row + i));
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const float4 v = load4(row + i);
+      store4(o + i, make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale));
+    }
   } else {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = jb::to_f32(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = jb::to_f32(row[i]) * scale;
   }
 }
 
@@ -207,17 +210,18 @@ __global__ void zero_f32_kernel(float4* __restrict__ p, size_t n4) {
 
 }  // namespace
 
-// ids[t] < 0 means: take feedback[token_slot[t]] (both may be null if no id is negative).
+// ids[t] < 0 means: take feedback[token_slot[t]] (both may be null if no id is negative).  The rows are multiplied by
+// `scale` in float32 (1: as stored).
 JB_EXPORT int jb_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H,
-                              const int* feedback, const int* token_slot, cudaStream_t stream) {
+                              const int* feedback, const int* token_slot, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   jb::Launch cfg(dim3(T), dim3(threads), 0, stream);
   cudaError_t e;
   if (table_dtype == JB_F32)
-    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<float>, (const float*)table, ids, out, H, feedback, token_slot);
+    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<float>, (const float*)table, ids, out, H, feedback, token_slot, scale);
   else if (table_dtype == JB_BF16)
-    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<bf16>, (const bf16*)table, ids, out, H, feedback, token_slot);
+    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<bf16>, (const bf16*)table, ids, out, H, feedback, token_slot, scale);
   else
     return JB_ERR_BAD_DTYPE;
   return (int)e;
@@ -421,17 +425,19 @@ JB_EXPORT int jb_pad_rows_bf16(const void* x, int K, void* out, int Kp, int T, c
 //   residual[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * gamma      (y: the sublayer's float32 output, may be null)
 //   x_out[t] = residual[t] in the engine dtype                         (the next sublayer's input, may be null)
 //   y[t] = 0                                                           (the next sublayer adds its output into it)
-// One block per token; `clear` as in the norms.  With y null it only casts; with x_out null it only adds.
+// One block per token; `clear` and `clear2` as `clear` in the norms.  With y null it only casts; with x_out null it only adds.
 // ---------------------------------------------------------------------------
 namespace {
 template <typename TG, typename TO>
 __global__ void sublayer_norm_add_kernel(float* __restrict__ y, const TG* __restrict__ gamma, float eps, float mult,
                                          float* __restrict__ residual, TO* __restrict__ x_out, int H,
-                                         float4* __restrict__ clear, size_t clear_n4) {
+                                         float4* __restrict__ clear, size_t clear_n4, float4* __restrict__ clear2,
+                                         size_t clear2_n4) {
   __shared__ float scratch[33];
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   clear_slice(clear, clear_n4);
+  clear_slice(clear2, clear2_n4);
   const size_t row = (size_t)blockIdx.x * H;
   float* res = residual + row;
   if (y == nullptr) {
@@ -456,11 +462,13 @@ template <typename TG, typename TO, int THREADS, int CACHE>
 __global__ void __launch_bounds__(THREADS) sublayer_norm_add_vec_kernel(float* __restrict__ y, const TG* __restrict__ gamma,
                                                                          float eps, float mult, float* __restrict__ residual,
                                                                          TO* __restrict__ x_out, int H,
-                                                                         float4* __restrict__ clear, size_t clear_n4) {
+                                                                         float4* __restrict__ clear, size_t clear_n4,
+                                                                         float4* __restrict__ clear2, size_t clear2_n4) {
   __shared__ float scratch[THREADS / 32];
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   clear_slice(clear, clear_n4);
+  clear_slice(clear2, clear2_n4);
   const size_t row = (size_t)blockIdx.x * H;
   float* res = residual + row;
   const int n4 = H >> 2;
@@ -505,23 +513,26 @@ __global__ void __launch_bounds__(THREADS) sublayer_norm_add_vec_kernel(float* _
 
 JB_EXPORT int jb_sublayer_norm_add(float* y, const void* gamma, int gamma_dtype, float eps, float mult, float* residual,
                                    void* x_out, int out_dtype, int T, int H, float* clear, long long clear_n,
-                                   cudaStream_t stream) {
+                                   float* clear2, long long clear2_n, cudaStream_t stream) {
   if (T <= 0) return 0;
-  JB_REFUSE(clear != nullptr && ((clear_n & 3) != 0 || ((uintptr_t)clear & 15) != 0),
-            "sublayer_norm_add: the buffer to clear is not made of whole 16-byte vectors");
+  JB_REFUSE((clear != nullptr && ((clear_n & 3) != 0 || ((uintptr_t)clear & 15) != 0)) ||
+                (clear2 != nullptr && ((clear2_n & 3) != 0 || ((uintptr_t)clear2 & 15) != 0)),
+            "sublayer_norm_add: a buffer to clear is not made of whole 16-byte vectors");
   JB_REFUSE(y == nullptr && x_out == nullptr, "sublayer_norm_add: nothing to do");
   float4* clear4 = (float4*)clear;
   const size_t clear_n4 = clear ? (size_t)clear_n >> 2 : 0;
+  float4* clear24 = (float4*)clear2;
+  const size_t clear2_n4 = clear2 ? (size_t)clear2_n >> 2 : 0;
   const bool vec = (H & 3) == 0, narrow = H <= 2048;
   jb::Launch cfg(dim3(T), dim3(vec ? (narrow ? 128 : 256) : (H >= 1024 ? 256 : 128)), 0, stream);
   cudaError_t e;
 #define JB_LAUNCH_SN(TG, TO)                                                                                        \
   e = !vec     ? cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_kernel<TG, TO>, y, (const TG*)gamma, eps, mult,      \
-                                    residual, (TO*)x_out, H, clear4, clear_n4)                                     \
+                                    residual, (TO*)x_out, H, clear4, clear_n4, clear24, clear2_n4)                 \
       : narrow ? cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_vec_kernel<TG, TO, 128, 4>, y, (const TG*)gamma, eps, \
-                                    mult, residual, (TO*)x_out, H, clear4, clear_n4)                               \
+                                    mult, residual, (TO*)x_out, H, clear4, clear_n4, clear24, clear2_n4)           \
                : cudaLaunchKernelEx(&cfg.c, sublayer_norm_add_vec_kernel<TG, TO, 256, 8>, y, (const TG*)gamma, eps, \
-                                    mult, residual, (TO*)x_out, H, clear4, clear_n4)
+                                    mult, residual, (TO*)x_out, H, clear4, clear_n4, clear24, clear2_n4)
   if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_SN(float, float);
   else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_SN(float, bf16);
   else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_SN(bf16, float);

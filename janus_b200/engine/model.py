@@ -98,14 +98,19 @@ class DecoderModel:
     def _forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
         T = ctx.n_tokens
         residual = ctx.workspace.get("residual", (T, self.streams * self.hidden_size), torch.float32)
+        transforms = self.embedding_transforms
         if self.streams == 1:
+            # a single embedding transform that only multiplies is done by the gather itself
+            scale = getattr(transforms[0], "plain_scale", lambda: None)() if len(transforms) == 1 else None
+            if scale is not None:
+                transforms = ()
             ops.embed_gather(self.embedding, ctx.token_ids, residual, ctx.feedback,
-                             ctx.seq_slot if ctx.feedback is not None else None)
+                             ctx.seq_slot if ctx.feedback is not None else None, scale=1.0 if scale is None else scale)
         else:
             # every stream starts as the embedding
             ops.embed_streams(self.embedding, ctx.token_ids, residual, self.streams, ctx.feedback,
                               ctx.seq_slot if ctx.feedback is not None else None)
-        for transform in self.embedding_transforms:
+        for transform in transforms:
             transform.forward(residual, ctx)
         ctx.pending_write = None
         for place, entry in enumerate(self.schedule):

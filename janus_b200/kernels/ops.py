@@ -53,7 +53,7 @@ def stream_scope():
 # the last argument of every function is the stream.  Declared once per library, so that a launch passes
 # plain Python integers and floats (a pointer is `tensor.data_ptr()`, None is a null pointer).
 _SIGNATURES = {
-    "jb_embed_gather": "pippiippp", "jb_rmsnorm": "pppifpiiiplp", "jb_residual_add": "ppilp",
+    "jb_embed_gather": "pippiippfp", "jb_rmsnorm": "pppifpiiiplp", "jb_residual_add": "ppilp",
     "jb_swiglu": "ppiiip", "jb_swiglu_f32_to_bf16": "piipiip", "jb_zero_f32": "plp",
     "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
     "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiifp",
@@ -69,7 +69,7 @@ _SIGNATURES = {
     "jb_diff_attention": "pppipipppiiiiiiiiiffffp",
     "jb_diff_attention_prefill": "pppppppiiiiiiiiiiffffp",
     "jb_clamped_glu": "piipiiiffp",
-    "jb_sublayer_norm_add": "ppiffppiiiplp", "jb_qk_norm_rope_cache": "pippppfpippipppiiiiiiip",
+    "jb_sublayer_norm_add": "ppiffppiiiplplp", "jb_qk_norm_rope_cache": "pippppfpippipppiiiiiiip",
     "jb_latent_prep": "piiiipfpippiip", "jb_causal_conv_silu": "piiippipllppppiiiip",
     "jb_mamba2_scan": "piiipipppppllppiiiiiiippp", "jb_gated_group_rmsnorm": "ppipfpiiiip", "jb_pad_rows_bf16": "pipiip", "jb_scale_softcap": "plffp",
 }
@@ -172,8 +172,9 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 
 # -- embedding, norm, elementwise ---------------------------------------------
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
-                 feedback: Optional[torch.Tensor] = None, token_slot: Optional[torch.Tensor] = None) -> None:
-    """out[t, :] = float32(table[ids[t], :]); a negative id stands for feedback[token_slot[t]]"""
+                 feedback: Optional[torch.Tensor] = None, token_slot: Optional[torch.Tensor] = None,
+                 scale: float = 1.0) -> None:
+    """out[t, :] = float32(table[ids[t], :]) * scale; a negative id stands for feedback[token_slot[t]]"""
     T, H = out.shape
     _need(table, "embed table")
     _need(ids, "token ids", torch.int32, (T,))
@@ -182,7 +183,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
         raise KernelError(f"embed: table width {table.shape[1]} != output width {H}")
     _check(_lib("elementwise").jb_embed_gather(
         _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), T, H, _ptr(feedback), _ptr(token_slot),
-        _stream()), "embed_gather")
+        float(scale), _stream()), "embed_gather")
 
 
 def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, out: torch.Tensor,
@@ -1153,10 +1154,10 @@ def pad_rows_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
 # -- a sublayer whose output is normed before it joins the residual stream ---------------------------------
 def sublayer_norm_add(y: Optional[torch.Tensor], gamma: Optional[torch.Tensor], eps: float, mult: float,
                       residual: torch.Tensor, x_out: Optional[torch.Tensor],
-                      clear: Optional[torch.Tensor] = None) -> None:
+                      clear: Optional[torch.Tensor] = None, clear2: Optional[torch.Tensor] = None) -> None:
     """residual += mult * y / sqrt(mean(y^2) + eps) * gamma (row by row; y float32, set to zero afterwards), then
-    x_out = residual in x_out's dtype.  y None: the cast alone; x_out None: the sum alone.  `clear`: a float32
-    scratch tensor (whole 16-byte vectors) that the same launch sets to zero."""
+    x_out = residual in x_out's dtype.  y None: the cast alone; x_out None: the sum alone.  `clear`, `clear2`: float32
+    scratch tensors (whole 16-byte vectors) that the same launch sets to zero."""
     T, H = residual.shape
     _need(residual, "residual", torch.float32)
     if y is not None:
@@ -1164,12 +1165,14 @@ def sublayer_norm_add(y: Optional[torch.Tensor], gamma: Optional[torch.Tensor], 
         _need(gamma, "norm weight", None, (H,))
     if x_out is not None:
         _need(x_out, "sublayer input", None, (T, H))
-    if clear is not None:
-        _need(clear, "buffer to clear", torch.float32)
+    for c in (clear, clear2):
+        if c is not None:
+            _need(c, "buffer to clear", torch.float32)
     _check(_lib("elementwise").jb_sublayer_norm_add(
         _ptr(y), _ptr(gamma) if y is not None else None, dtype_code(gamma.dtype) if y is not None else F32, eps, mult,
         _ptr(residual), _ptr(x_out), dtype_code(x_out.dtype) if x_out is not None else F32, T, H, _ptr(clear),
-        0 if clear is None else clear.numel(), _stream()), "sublayer_norm_add")
+        0 if clear is None else clear.numel(), _ptr(clear2), 0 if clear2 is None else clear2.numel(), _stream()),
+        "sublayer_norm_add")
 
 
 # -- attention mixers whose queries and keys are normed over the whole projection ----------------------------

@@ -239,9 +239,10 @@ class Norm(Part):
         raise NotImplementedError
 
     def add_normed(self, y: Optional[torch.Tensor], residual: torch.Tensor, mult: float,
-                   x_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+                   x_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None,
+                   clear2: Optional[torch.Tensor] = None) -> None:
         """residual += mult * norm(y) for a sublayer's float32 output y (set to zero afterwards), then
-        x_out = residual in x_out's dtype, in one launch; `clear` as in `forward`.  Needed only by arrangements
+        x_out = residual in x_out's dtype, in one launch; `clear` and `clear2` as `clear` in `forward`.  Needed only by arrangements
         that norm a sublayer's output instead of its input."""
         raise NotImplementedError
 

@@ -155,11 +155,11 @@ class OutputNormBlock:
         else:
             if pending is not None:
                 pending[0].write(residual, pending[1])
-            if y.numel() % 4 == 0:
-                ops.zero_f32(y)
+            if y.numel() % 4 == 0:          # the cast's launch also zeroes the sublayers' buffer
+                self.mixer_norm.add_normed(None, residual, self.mult, x_out=x, clear=scratch, clear2=y)
             else:
                 y.zero_()
-            self.mixer_norm.add_normed(None, residual, self.mult, x_out=x, clear=scratch)
+                self.mixer_norm.add_normed(None, residual, self.mult, x_out=x, clear=scratch)
         if scratch is not None:
             self.mixer.forward(x, y, ctx, cache_view, writes_cache, scratch_cleared=True)
         else:

@@ -34,9 +34,10 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.gamma, self.eps, out, row_index, clear)
 
     def add_normed(self, y: Optional[torch.Tensor], residual: torch.Tensor, mult: float,
-                   x_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+                   x_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None,
+                   clear2: Optional[torch.Tensor] = None) -> None:
         """residual += mult * norm(y), y <- 0, x_out = residual in its dtype (y None: only that), one launch."""
-        ops.sublayer_norm_add(y, self.gamma, self.eps, mult, residual, x_out, clear)
+        ops.sublayer_norm_add(y, self.gamma, self.eps, mult, residual, x_out, clear, clear2)
 
     def forward_streams(self, x: torch.Tensor, streams: int, weights: Optional[torch.Tensor], out: torch.Tensor,
                         row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None,

@@ -19,6 +19,11 @@ class ScaleSoftCap(Transform):
         if cap is not None and not self.cap > 0.0:
             raise ValueError(f"a soft cap must be positive, got {cap}")
 
+    def plain_scale(self):
+        """The factor, if this transform is a multiplication and nothing else (the model then multiplies where
+        it makes the tensor, without a launch of this transform's own); else None."""
+        return self.scale if self.cap == 0.0 else None
+
     def forward(self, t: torch.Tensor, ctx) -> None:
         ops.scale_softcap(t, self.scale, self.cap)
 

@@ -257,9 +257,10 @@ def test_output_norm_sum_and_the_gelu_gate_against_their_formulas():
         for out_dtype in (torch.float32, torch.bfloat16):
             rd, yd = dev(res), dev(y)
             x = torch.empty(T, H, dtype=out_dtype, device="cuda")
-            clear = torch.ones(8, 4, device="cuda")
-            ops.sublayer_norm_add(yd, dev(gamma), 1e-5, mult, rd, x, clear)
-            assert rel_err(rd.cpu(), want) < 1e-5 and float(yd.abs().sum()) == 0.0 and float(clear.abs().sum()) == 0.0
+            clear, clear2 = torch.ones(8, 4, device="cuda"), torch.ones(3, 12, device="cuda")
+            ops.sublayer_norm_add(yd, dev(gamma), 1e-5, mult, rd, x, clear, clear2)
+            assert rel_err(rd.cpu(), want) < 1e-5 and float(yd.abs().sum()) == 0.0
+            assert float(clear.abs().sum()) == 0.0 and float(clear2.abs().sum()) == 0.0
             assert rel_err(x.float().cpu(), want) < (1e-5 if out_dtype == torch.float32 else 5e-3)
         rd, yd = dev(res), dev(y)
         ops.sublayer_norm_add(yd, dev(gamma, torch.bfloat16), 1e-5, mult, rd, None)         # the sum alone
@@ -267,6 +268,11 @@ def test_output_norm_sum_and_the_gelu_gate_against_their_formulas():
         x = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
         ops.sublayer_norm_add(None, None, 0.0, 0.0, rd, x)                                  # the cast alone
         assert torch.equal(x.cpu(), rd.cpu().to(torch.bfloat16))
+    for H in (40, 33):                  # the embedding's scale in the gather's own launch
+        table = torch.randn(20, H, generator=g).to(torch.bfloat16)
+        out = torch.empty(4, H, device="cuda")
+        ops.embed_gather(table.cuda(), i32([3, 19, 0, 3]), out, scale=2.5)
+        assert rel_err(out.cpu(), table[[3, 19, 0, 3]].to(P.DT) * 2.5) < 1e-6
     gu = torch.randn(6, 50, generator=g) * 3
     act = torch.empty(6, 20, device="cuda")
     ops.clamped_glu(dev(gu), act, 30, ops.GELU_TANH_GATE, 1.0)
